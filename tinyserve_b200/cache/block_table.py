@@ -2,7 +2,9 @@
 
 Position ``p`` lives in ``pages[p // page_size]`` at offset ``p % page_size`` (upstream
 src/tinyserve/block_table.py:19-89). For a group that only needs a window of the positions,
-pages the window has passed are given back early and their entries become ``RELEASED``.
+pages the window has passed are given back early and their entries become ``RELEASED``;
+pages that hold any of the first ``keep_first`` positions (which stay visible whatever the window)
+are never given back early.
 """
 
 from __future__ import annotations
@@ -15,15 +17,16 @@ RELEASED = -1
 
 
 class BlockTable:
-    def __init__(self, allocator: PageAllocator, page_size: int, window: int | None = None) -> None:
+    def __init__(self, allocator: PageAllocator, page_size: int, window: int | None = None, keep_first: int = 0) -> None:
         if page_size <= 0:
             raise ValueError(f"page_size must be positive, got {page_size}")
         self.allocator = allocator
         self.page_size = page_size
         self.window = window
+        self.kept_pages = -(-max(int(keep_first), 0) // page_size)    # pages at the front that a window never drops
         self.pages: list[int] = []
         self.num_tokens = 0
-        self._first_live = 0       # entries before this index are RELEASED
+        self._first_live = 0       # entries before this index (and from ``kept_pages`` on) are RELEASED
         # int32 mirror of ``pages`` for building device block tables without a Python loop;
         # released entries hold 0 there (a valid page id that the kernels never look at).
         self._mirror = np.zeros(16, dtype=np.int32)
@@ -82,10 +85,11 @@ class BlockTable:
         if first_needed <= 0:
             return 0
         upto = min(first_needed // self.page_size, len(self.pages))
-        gone = [p for p in self.pages[self._first_live:upto] if p != RELEASED]
+        first = max(self._first_live, self.kept_pages)
+        gone = [p for p in self.pages[first:upto] if p != RELEASED]
         if gone:
             self.allocator.free(gone)
-        for i in range(self._first_live, upto):
+        for i in range(first, upto):
             self.pages[i] = RELEASED
             self._mirror[i] = 0
         self._first_live = max(self._first_live, upto)

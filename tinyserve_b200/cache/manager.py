@@ -69,7 +69,8 @@ class PageGroup:
         window has passed are given back after the step)."""
         pages = -(-num_tokens // self.page_size)
         if self.need.window is not None:
-            pages = min(pages, -(-(self.need.window + min(step_tokens, num_tokens)) // self.page_size) + 1)
+            kept = -(-self.need.keep_first // self.page_size)
+            pages = min(pages, -(-(self.need.window + min(step_tokens, num_tokens)) // self.page_size) + 1 + kept)
         return pages
 
 
@@ -127,7 +128,7 @@ class CacheManager:
             if max_step_tokens is not None:
                 for i, need in enumerate(distinct):
                     if need.window is not None:
-                        per_request = -(-(need.window + max_step_tokens) // page_size) + 1
+                        per_request = -(-(need.window + max_step_tokens) // page_size) + 1 + -(-need.keep_first // page_size)
                         sizes[i] = min(num_pages, max_requests * per_request)
         else:
             sizes = [int(n) for n in num_pages]
@@ -199,7 +200,7 @@ class CacheManager:
             slot = self.state_pool.allocate()
             for storage in self._slot_storage:
                 storage[slot].zero_()
-        tables = [BlockTable(g.allocator, g.page_size, g.need.window) for g in self.groups]
+        tables = [BlockTable(g.allocator, g.page_size, g.need.window, g.need.keep_first) for g in self.groups]
         self._next_uid += 1
         return RequestCache(tables, slot, uid=self._next_uid)
 

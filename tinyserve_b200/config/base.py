@@ -48,6 +48,7 @@ class LayerSpec:
     block: str
     parts: Mapping[str, PartSpec]
     position: PartSpec | None = None  # position encoding the mixers apply; None = none
+    block_args: Mapping[str, Any] = field(default_factory=dict)   # constants of the block itself
 
 
 @dataclass(frozen=True)

@@ -26,6 +26,7 @@ struct AttnArgs {
   // Optional extras (kernels that do not know them leave them at their defaults).
   const float* sinks = nullptr;  // [num_heads] a logit per head that joins the softmax's denominator without a value
   int v_head_dim = 0;            // size of a value head when it differs from head_dim (0: the same)
+  int keep_first = 0;            // with a window: positions below this stay visible to every later query
 };
 
 // The finished row: num / den, where the denominator also takes 2^(sink - max) when the head has

@@ -12,15 +12,16 @@ extern "C" int ts_paged_attention_simt(
     int table_width, const int* cu_q, const int* ctx_lens, const int* decode_seqs, int num_decode,
     const int* prefill_seqs, int num_prefill, int max_query_len, int num_heads, int num_kv_heads,
     int head_dim, int page_size, float scale, int window, int num_splits, float* part_acc,
-    float* part_ml, const float* sinks, int v_head_dim, int dtype, cudaStream_t stream) {
+    float* part_ml, const float* sinks, int v_head_dim, int keep_first, int dtype, cudaStream_t stream) {
   // `sinks` (optional, [num_heads] float): a logit per head that joins the softmax's denominator
   // without a value. `v_head_dim` (0 = head_dim): the size of a value head; when it differs from
   // head_dim the caches have different row sizes and `out` is [T, num_heads * v_head_dim].
+  // `keep_first` (with a window): positions below it stay visible to every later query.
   // The tiled kernel takes any head size up to 256; the split-K kernel sizes in steps of 16.
   if (head_dim <= 0 || head_dim > 256) return TS_ERR_UNSUPPORTED;
   if (v_head_dim == head_dim) v_head_dim = 0;
   if (v_head_dim < 0 || v_head_dim > 256) return TS_ERR_UNSUPPORTED;
-  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || page_size <= 0 || window < 0) return TS_ERR_BAD_ARGUMENT;
+  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || page_size <= 0 || window < 0 || keep_first < 0) return TS_ERR_BAD_ARGUMENT;
   if (dtype != TS_DTYPE_F32 && dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
   AttnArgs a;
   a.q = q; a.out = out; a.k_cache = k_cache; a.v_cache = v_cache;
@@ -30,7 +31,7 @@ extern "C" int ts_paged_attention_simt(
   a.scale_log2 = scale * 1.4426950408889634f;
   a.window = window;
   a.num_splits = 1; a.part_acc = nullptr; a.part_ml = nullptr;
-  a.sinks = sinks; a.v_head_dim = v_head_dim;
+  a.sinks = sinks; a.v_head_dim = v_head_dim; a.keep_first = window > 0 ? keep_first : 0;
   int st = 0;
   if (num_prefill > 0) {
     a.seq_ids = prefill_seqs; a.num_seqs = num_prefill;

@@ -2,7 +2,8 @@
 // the fallback for head sizes the tensor-core kernels do not take.
 //
 // Math (upstream src/tinyserve/attention.py:89-111): s = scale * q.k over head_dim in 32-bit,
-// causal mask (key position <= query position; optionally > query position - window),
+// causal mask (key position <= query position; optionally > query position - window, or
+// below `keep_first`: the first positions that a window never drops),
 // softmax in 32-bit (online, base 2), o = sum p v in 32-bit, cast once to the output type.
 // Query head h reads kv head h / (num_heads / num_kv_heads).
 //
@@ -80,11 +81,14 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
   int k_lo = 0;
   if (a.window > 0) k_lo = max(0, qpos_first - a.window + 1);
   const int k_begin = (k_lo / PF_TK) * PF_TK;
+  // with kept first positions the tiles below the window that hold any of them come first
+  const int kept = (a.window > 0) ? min(a.keep_first, k_lo) : 0;
+  const int kept_end = min(k_begin, ((kept + PF_TK - 1) / PF_TK) * PF_TK);
   constexpr int VEC = Vec<T>::N;
   const int chunks = D / VEC, vchunks = DV / VEC;
   const bool vec_ok = (D % VEC == 0) && (DV % VEC == 0);
 
-  for (int k0 = k_begin; k0 <= qpos_last; k0 += PF_TK) {
+  for (int k0 = kept_end > 0 ? 0 : k_begin; k0 <= qpos_last; k0 = (k0 + PF_TK == kept_end) ? k_begin : k0 + PF_TK) {
     __syncthreads();   // previous tile fully consumed (and Qs/row state initialised)
     // ---- stage keys and values k0 .. k0+TK-1 (zeros outside the request's visible range)
     if (vec_ok) {
@@ -94,7 +98,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
         const int cc = is_key ? c : c - chunks;
         const int kpos = k0 + kk;
         float f[VEC];
-        if (kpos >= k_lo && kpos <= qpos_last) {
+        if ((kpos >= k_lo || kpos < kept) && kpos <= qpos_last) {
           const size_t row = kv_row_of(table, kpos, kvh, a);
           Vec<T> raw;
           raw.load(is_key ? kc + row * D + (size_t)cc * VEC : vc + row * DV + (size_t)cc * VEC);
@@ -115,7 +119,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
         const int cc = is_key ? c : c - D;
         const int kpos = k0 + kk;
         float f = 0.f;
-        if (kpos >= k_lo && kpos <= qpos_last) {
+        if ((kpos >= k_lo || kpos < kept) && kpos <= qpos_last) {
           const size_t row = kv_row_of(table, kpos, kvh, a);
           f = is_key ? to_float(kc[row * D + cc]) : to_float(vc[row * DV + cc]);
         }
@@ -144,7 +148,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_attn_kernel(AttnArgs a) {
       for (int j = 0; j < 2; ++j) {
         const int kpos = k0 + tx * 2 + j;
         bool ok = (r < nq) && (kpos <= qpos);
-        if (a.window > 0) ok = ok && (kpos > qpos - a.window);
+        if (a.window > 0) ok = ok && (kpos > qpos - a.window || kpos < a.keep_first);
         Ss[r * (PF_TK + 1) + tx * 2 + j] = ok ? s[i][j] : NEG_INF;
       }
     }
@@ -253,10 +257,13 @@ __global__ void __launch_bounds__(DC_THREADS) decode_attn_kernel(AttnArgs a, int
   const int ctx = a.ctx_lens[seq];
   const int qrow = a.cu_q[seq];
   const int lo = (a.window > 0) ? max(0, ctx - a.window) : 0;
-  const int len = ctx - lo;
+  // the visible keys in one run of indices: the kept first positions below the window, then the window
+  const int kept = min(a.keep_first, lo);
+  const int gap = lo - kept;
+  const int len = ctx - gap;
   const int per = (len + a.num_splits - 1) / a.num_splits;
-  const int k_begin = lo + split * per;
-  const int k_end = min(ctx, k_begin + per);
+  const int k_begin = split * per;
+  const int k_end = min(len, k_begin + per);
   const int* table = a.block_tables + (size_t)seq * a.table_width;
   const T* kc = (const T*)a.k_cache;
   const T* vc = (const T*)a.v_cache;
@@ -297,10 +304,10 @@ __global__ void __launch_bounds__(DC_THREADS) decode_attn_kernel(AttnArgs a, int
     bool valid[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int kpos = base + u * KPW + sub;
-      valid[u] = kpos < k_end;
+      const int kidx = base + u * KPW + sub;
+      valid[u] = kidx < k_end;
       size_t off = 0;
-      if (valid[u]) off = kv_offset_of(table, kpos, kvh, a);
+      if (valid[u]) off = kv_offset_of(table, kidx < kept ? kidx : kidx + gap, kvh, a);
 #pragma unroll
       for (int c = 0; c < CPL; ++c) {
         const int chunk = lk + c * LPK;

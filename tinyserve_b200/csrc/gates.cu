@@ -18,23 +18,46 @@ __device__ __forceinline__ float activate(float z) {
   return 0.5f * z * (1.f + tanhf(inner));
 }
 
-// out[t, j] = act(gate_up[t, j]) * gate_up[t, I + j]
+// out[t, j] = act(gate_up[t, j] + bias[j]) * (gate_up[t, I + j] + bias[I + j])   (bias optional)
 // ACT_CLAMPED_SWISH: g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(1.702 g) (u + 1)
 template <typename T, int ACT>
-__global__ void act_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total, float limit) {
+__global__ void act_mul_kernel(const T* __restrict__ gate_up, const T* __restrict__ bias, T* __restrict__ out, int inter,
+                               size_t total, float limit) {
   pdl_trigger();
   pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / inter;
     const int j = (int)(idx - t * inter);
     const T* row = gate_up + t * 2 * (size_t)inter;
+    float gate = to_float(row[j]), up = to_float(row[inter + j]);
+    if (bias) {
+      gate += to_float(bias[j]);
+      up += to_float(bias[inter + j]);
+    }
     if (ACT == ACT_CLAMPED_SWISH) {
-      const float g = fminf(to_float(row[j]), limit);
-      const float u = fminf(fmaxf(to_float(row[inter + j]), -limit), limit);
+      const float g = fminf(gate, limit);
+      const float u = fminf(fmaxf(up, -limit), limit);
       out[idx] = from_float<T>(g * sigmoidf(1.702f * g) * (u + 1.f));
     } else {
-      out[idx] = from_float<T>(activate<ACT>(to_float(row[j])) * to_float(row[inter + j]));
+      out[idx] = from_float<T>(activate<ACT>(gate) * up);
     }
+  }
+}
+
+// out[t, j] = act(x[t, j]) * table[rows[t], col0 + j]: a gate on a row that is looked up per token
+// (x rows are `x_stride` apart, table rows `table_width`); a row index outside the table gives NaN.
+template <typename T, int ACT>
+__global__ void act_mul_gather_kernel(const T* __restrict__ x, int x_stride, const int* __restrict__ rows,
+                                      const T* __restrict__ table, int table_rows, int table_width, int col0,
+                                      T* __restrict__ out, int n, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / n;
+    const int j = (int)(idx - t * n);
+    const int r = rows[t];
+    const float e = (r >= 0 && r < table_rows) ? to_float(table[(size_t)r * table_width + col0 + j]) : __int_as_float(0x7fc00000);
+    out[idx] = from_float<T>(activate<ACT>(to_float(x[t * x_stride + j])) * e);
   }
 }
 
@@ -48,13 +71,14 @@ __global__ void softcap_kernel(float* __restrict__ x, float cap, float inv_cap, 
 
 // One warp per (token, head): y = x / sqrt(mean(x^2) + eps) when `normalise`, times
 // weight[head * weight_head_stride + c] when a weight is given, times sigmoid(gate[t, head, c])
-// when a gate is given (`gate_per_head`: sigmoid(gate[t, head]), one value for the whole head).
+// when a gate is given (`gate_per_head`: sigmoid(gate[t, head]), one value for the whole head;
+// `gate_silu`: the gate's value is z sigmoid(z) instead of sigmoid(z)).
 // x is [T, heads, width] of type IN; gate rows are `gate_stride` apart.
 template <typename IN, typename T>
 __global__ void head_norm_gate_kernel(const IN* __restrict__ x, const T* __restrict__ weight, int weight_head_stride,
                                       const T* __restrict__ gate, int gate_stride, T* __restrict__ out,
                                       int num_tokens, int heads, int width, int normalise, float eps,
-                                      int gate_per_head) {
+                                      int gate_per_head, int gate_silu) {
   pdl_trigger();
   pdl_wait();
   const int warp = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
@@ -71,11 +95,18 @@ __global__ void head_norm_gate_kernel(const IN* __restrict__ x, const T* __restr
     ss = warp_sum(ss);
     rstd = rsqrtf(ss / (float)width + eps);
   }
-  const float head_gate = (gate && gate_per_head) ? sigmoidf(to_float(gate[(size_t)t * gate_stride + h])) : 1.f;
+  float head_gate = 1.f;
+  if (gate && gate_per_head) {
+    const float z = to_float(gate[(size_t)t * gate_stride + h]);
+    head_gate = gate_silu ? z * sigmoidf(z) : sigmoidf(z);
+  }
   for (int c = lane; c < width; c += 32) {
     float v = to_float(xr[c]) * rstd * head_gate;
     if (weight) v *= to_float(weight[h * weight_head_stride + c]);
-    if (gate && !gate_per_head) v *= sigmoidf(to_float(gate[(size_t)t * gate_stride + h * width + c]));
+    if (gate && !gate_per_head) {
+      const float z = to_float(gate[(size_t)t * gate_stride + h * width + c]);
+      v *= gate_silu ? z * sigmoidf(z) : sigmoidf(z);
+    }
     out[(size_t)warp * width + c] = from_float<T>(v);
   }
 }
@@ -90,15 +121,15 @@ static int blocks_for(size_t total, int threads) {
   return (int)b;
 }
 
-extern "C" int ts_act_mul(const void* gate_up, void* out, int num_tokens, int inter, int activation, float limit,
-                          int dtype, cudaStream_t stream) {
+extern "C" int ts_act_mul(const void* gate_up, const void* bias, void* out, int num_tokens, int inter, int activation,
+                          float limit, int dtype, cudaStream_t stream) {
   const size_t total = (size_t)num_tokens * inter;
   if (total == 0) return 0;
   if (activation != ACT_SILU && activation != ACT_GELU_TANH && activation != ACT_CLAMPED_SWISH) return TS_ERR_BAD_ARGUMENT;
   if (activation == ACT_CLAMPED_SWISH && !(limit > 0.f)) return TS_ERR_BAD_ARGUMENT;
   const int b = blocks_for(total, 256);
 #define TS_ACT_CASE(T_, ACT_) \
-  return launch(act_mul_kernel<T_, ACT_>, b, 256, 0, stream, (const T_*)gate_up, (T_*)out, inter, total, limit)
+  return launch(act_mul_kernel<T_, ACT_>, b, 256, 0, stream, (const T_*)gate_up, (const T_*)bias, (T_*)out, inter, total, limit)
   if (dtype == TS_DTYPE_F32) {
     if (activation == ACT_SILU) TS_ACT_CASE(float, ACT_SILU);
     if (activation == ACT_CLAMPED_SWISH) TS_ACT_CASE(float, ACT_CLAMPED_SWISH);
@@ -113,6 +144,29 @@ extern "C" int ts_act_mul(const void* gate_up, void* out, int num_tokens, int in
   return TS_ERR_BAD_ARGUMENT;
 }
 
+extern "C" int ts_act_mul_gather(const void* x, int x_stride, const int* rows, const void* table, int table_rows,
+                                 int table_width, int col0, void* out, int num_tokens, int n, int activation, int dtype,
+                                 cudaStream_t stream) {
+  const size_t total = (size_t)num_tokens * n;
+  if (total == 0) return 0;
+  if (activation != ACT_SILU && activation != ACT_GELU_TANH) return TS_ERR_BAD_ARGUMENT;
+  if (col0 < 0 || col0 + n > table_width || x_stride < n) return TS_ERR_BAD_ARGUMENT;
+  const int b = blocks_for(total, 256);
+#define TS_GATHER_CASE(T_, ACT_)                                                                                      \
+  return launch(act_mul_gather_kernel<T_, ACT_>, b, 256, 0, stream, (const T_*)x, x_stride, rows, (const T_*)table, \
+                table_rows, table_width, col0, (T_*)out, n, total)
+  if (dtype == TS_DTYPE_F32) {
+    if (activation == ACT_SILU) TS_GATHER_CASE(float, ACT_SILU);
+    TS_GATHER_CASE(float, ACT_GELU_TANH);
+  }
+  if (dtype == TS_DTYPE_BF16) {
+    if (activation == ACT_SILU) TS_GATHER_CASE(bf16, ACT_SILU);
+    TS_GATHER_CASE(bf16, ACT_GELU_TANH);
+  }
+#undef TS_GATHER_CASE
+  return TS_ERR_BAD_ARGUMENT;
+}
+
 extern "C" int ts_softcap(float* x, size_t total, float cap, cudaStream_t stream) {
   if (total == 0) return 0;
   if (!(cap > 0.f)) return TS_ERR_BAD_ARGUMENT;
@@ -121,18 +175,19 @@ extern "C" int ts_softcap(float* x, size_t total, float cap, cudaStream_t stream
 
 extern "C" int ts_head_norm_gate(const void* x, int x_is_f32, const void* weight, int weight_head_stride,
                                  const void* gate, int gate_stride, void* out, int num_tokens, int heads, int width,
-                                 int normalise, float eps, int gate_per_head, int dtype, cudaStream_t stream) {
+                                 int normalise, float eps, int gate_per_head, int gate_silu, int dtype,
+                                 cudaStream_t stream) {
   const size_t warps = (size_t)num_tokens * heads;
   if (warps == 0) return 0;
   const int threads = 128;
   const int b = (int)((warps * 32 + threads - 1) / threads);
   if (dtype == TS_DTYPE_F32)
     return launch(head_norm_gate_kernel<float, float>, b, threads, 0, stream, (const float*)x, (const float*)weight,
-                  weight_head_stride, (const float*)gate, gate_stride, (float*)out, num_tokens, heads, width, normalise, eps, gate_per_head);
+                  weight_head_stride, (const float*)gate, gate_stride, (float*)out, num_tokens, heads, width, normalise, eps, gate_per_head, gate_silu);
   if (dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
   if (x_is_f32)
     return launch(head_norm_gate_kernel<float, bf16>, b, threads, 0, stream, (const float*)x, (const bf16*)weight,
-                  weight_head_stride, (const bf16*)gate, gate_stride, (bf16*)out, num_tokens, heads, width, normalise, eps, gate_per_head);
+                  weight_head_stride, (const bf16*)gate, gate_stride, (bf16*)out, num_tokens, heads, width, normalise, eps, gate_per_head, gate_silu);
   return launch(head_norm_gate_kernel<bf16, bf16>, b, threads, 0, stream, (const bf16*)x, (const bf16*)weight,
-                weight_head_stride, (const bf16*)gate, gate_stride, (bf16*)out, num_tokens, heads, width, normalise, eps, gate_per_head);
+                weight_head_stride, (const bf16*)gate, gate_stride, (bf16*)out, num_tokens, heads, width, normalise, eps, gate_per_head, gate_silu);
 }

@@ -89,31 +89,7 @@ __global__ void hc_mix_norm_kernel(float* __restrict__ lanes, const float* __res
 
 // The same for a lane count known at compile time and rows of a multiple of four 16-byte-aligned
 // values: the connection weights sit in registers and every access is 16 bytes wide (8 for bf16).
-template <typename T> struct Quad;
-template <> struct Quad<float> {
-  static __device__ __forceinline__ void load(const float* p, float* f) {
-    const float4 v = *reinterpret_cast<const float4*>(p);
-    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
-  }
-  static __device__ __forceinline__ void store(float* p, const float* f) {
-    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
-  }
-};
-template <> struct Quad<bf16> {
-  static __device__ __forceinline__ void load(const bf16* p, float* f) {
-    const uint2 v = *reinterpret_cast<const uint2*>(p);
-    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
-    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
-  }
-  static __device__ __forceinline__ void store(bf16* p, const float* f) {
-    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
-    uint2 v;
-    v.x = *reinterpret_cast<uint32_t*>(&a);
-    v.y = *reinterpret_cast<uint32_t*>(&b);
-    *reinterpret_cast<uint2*>(p) = v;
-  }
-};
-
+// (Quad: four neighbouring elements in one access, common.cuh.)
 template <typename T, int S>
 __global__ void hc_mix_norm_vec_kernel(float* __restrict__ lanes, const float* __restrict__ fresh,
                                        const T* __restrict__ delta, const float* __restrict__ mix_prev,

@@ -1,0 +1,284 @@
+// Linear-attention mixers whose state is a matrix S [d x dv] per (request, head) in a slot of
+// 32-bit floats, without a correction term: the state of a token depends on the one before only
+// through a decay, so a token's chain is one multiply-add per element.
+//
+//  * MODE_BONUS (time mixing in the manner of RWKV-6): a decay per key channel and token,
+//    w = exp(-exp(w_pre + w_0)); the read-out comes first and sees the current token only through a
+//    bonus u per key channel: o = (S + diag(u) k v^T)^T r; then S <- diag(w) S + k v^T.
+//  * MODE_DECAY (linear attention with a constant decay per head): q, k, v pass SiLU;
+//    S <- decay_h S + k v^T; o = S^T q (the read-out sees the current token's write).
+//
+// Work split as in the other recurrent kernels: a CTA owns (request, head, block of 32 value
+// columns); compute warp w owns key rows [w * RPT, (w + 1) * RPT) and lane c column c, so a thread
+// keeps RPT elements of S in registers. Four loader warps stage the next chunk of tokens in shared
+// memory as 32-bit values (activations, decays) while the compute warps walk the current one. The
+// parts of a token's read-out (one per compute warp) wait in shared memory until the chunk is done.
+// Prompt portions and single decoded tokens are the same kernel.
+//
+// Also here: the token shift in front of the time mixing, out_m = h + (h_prev - h) * mu_m for
+// several mixes m, where h_prev of a request's first token of the step comes from its state slot
+// (zero at the request's start) and the slot then takes the step's last h.
+#define TS_PDL_CLASS PDL_OTHER
+#include "common.cuh"
+
+namespace ts {
+
+constexpr int LIN_MAX_KEY_DIM = 256;
+constexpr int LIN_LOADER_WARPS = 4;
+constexpr int LIN_LOADS = 8;
+constexpr int LIN_RPT = 32;
+constexpr int MODE_BONUS = 0, MODE_DECAY = 1;
+
+__device__ __forceinline__ float siluf(float z) { return z / (1.f + expf(-z)); }
+
+struct LinScanArgs {
+  const void* q; int q_stride;      // [T, H * d] rows q_stride apart (r of the time mixing)
+  const void* k; int k_stride;      // [T, H * d]
+  const void* v; int v_stride;      // [T, H * dv]
+  const float* w_pre; int w_stride; // MODE_BONUS: [T, H * d] decay pre-activations
+  const float* w_bias;              // MODE_BONUS: [H * d]
+  const float* bonus;               // MODE_BONUS: [H * d]
+  const float* decay;               // MODE_DECAY: [H]
+  float* state; int state_stride;   // [slots, H * d * dv]
+  const int* cu_q; const int* state_slots;
+  int H, d, dv;
+  float* out;                       // [T, H, dv]
+  int W, CH;
+};
+
+template <typename T, int MODE>
+__global__ void linear_scan_kernel(LinScanArgs a) {
+  extern __shared__ __align__(16) float sm[];
+  constexpr int RPT = LIN_RPT;
+  constexpr int NARR = MODE == MODE_BONUS ? 3 : 2;
+  const int W = a.W, CH = a.CH, d = a.d, dv = a.dv, H = a.H;
+  const int dpad = W * RPT;
+  const int buf_floats = CH * (NARR * dpad + 32);
+  float* part = sm + 2 * buf_floats;            // [CH][W][32]
+  const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * 32;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_trigger();
+  pdl_wait();
+  const int start = a.cu_q[b], end = a.cu_q[b + 1];
+  if (end <= start) return;
+  const int chunks = (end - start + CH - 1) / CH;
+  const bool loader = warp >= W;
+  const T* qp = (const T*)a.q;
+  const T* kp = (const T*)a.k;
+  const T* vp = (const T*)a.v;
+
+  auto load_chunk = [&](int c) {
+    float* q_s = sm + (c & 1) * buf_floats;
+    float* k_s = q_s + CH * dpad;
+    float* w_s = k_s + CH * dpad;                       // MODE_BONUS only
+    float* v_s = q_s + NARR * CH * dpad;
+    const int t0 = start + c * CH, nt = min(CH, end - t0);
+    const int lt = tid - W * 32, ln = LIN_LOADER_WARPS * 32;
+    for (int base = lt; base < nt * dpad; base += ln * LIN_LOADS) {
+      float qv[LIN_LOADS], kv[LIN_LOADS], wv[LIN_LOADS];
+#pragma unroll
+      for (int u = 0; u < LIN_LOADS; ++u) {
+        const int idx = base + u * ln;
+        const int tok = idx / dpad, r = idx - tok * dpad;
+        const bool ok = idx < nt * dpad && r < d;
+        qv[u] = ok ? to_float(qp[(size_t)(t0 + tok) * a.q_stride + h * d + r]) : 0.f;
+        kv[u] = ok ? to_float(kp[(size_t)(t0 + tok) * a.k_stride + h * d + r]) : 0.f;
+        if (MODE == MODE_BONUS) wv[u] = ok ? a.w_pre[(size_t)(t0 + tok) * a.w_stride + h * d + r] + a.w_bias[h * d + r] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < LIN_LOADS; ++u) {
+        const int idx = base + u * ln;
+        if (idx < nt * dpad) {
+          if (MODE == MODE_DECAY) {
+            q_s[idx] = siluf(qv[u]);
+            k_s[idx] = siluf(kv[u]);
+          } else {
+            q_s[idx] = qv[u];
+            k_s[idx] = kv[u];
+            w_s[idx] = expf(-expf(wv[u]));
+          }
+        }
+      }
+    }
+    for (int idx = lt; idx < nt * 32; idx += ln) {
+      const int tok = idx >> 5, c2 = idx & 31;
+      float x = (c0 + c2 < dv) ? to_float(vp[(size_t)(t0 + tok) * a.v_stride + h * dv + c0 + c2]) : 0.f;
+      if (MODE == MODE_DECAY) x = siluf(x);
+      v_s[idx] = x;
+    }
+  };
+
+  const int slot = a.state_slots[b];
+  const int col = c0 + lane;
+  const bool col_ok = col < dv;
+  float* S = a.state + (size_t)slot * a.state_stride + (size_t)h * d * dv;
+  const int r0 = warp * RPT;
+  float s[RPT], u[MODE == MODE_BONUS ? RPT : 1];
+  float decay = 1.f;
+  if (!loader) {
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) s[i] = (r0 + i < d && col_ok) ? S[(size_t)(r0 + i) * dv + col] : 0.f;
+    if (MODE == MODE_BONUS) {
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) u[i] = (r0 + i < d) ? a.bonus[h * d + r0 + i] : 0.f;
+    } else {
+      decay = a.decay[h];
+    }
+  } else {
+    load_chunk(0);
+  }
+  __syncthreads();
+  for (int c = 0; c < chunks; ++c) {
+    if (loader) {
+      if (c + 1 < chunks) load_chunk(c + 1);
+    } else {
+      const float* q_s = sm + (c & 1) * buf_floats;
+      const float* k_s = q_s + CH * dpad;
+      const float* w_s = k_s + CH * dpad;
+      const float* v_s = q_s + NARR * CH * dpad;
+      const int t0 = start + c * CH, nt = min(CH, end - t0);
+      for (int tok = 0; tok < nt; ++tok) {
+        const float4* q4 = reinterpret_cast<const float4*>(q_s + tok * dpad + r0);
+        const float4* k4 = reinterpret_cast<const float4*>(k_s + tok * dpad + r0);
+        const float4* w4 = reinterpret_cast<const float4*>(w_s + tok * dpad + r0);
+        const float vv = v_s[tok * 32 + lane];
+        float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < RPT / 4; ++i) {
+          const float4 kk = k4[i], qq = q4[i];
+          const float kx[4] = {kk.x, kk.y, kk.z, kk.w}, qx[4] = {qq.x, qq.y, qq.z, qq.w};
+          if (MODE == MODE_BONUS) {
+            const float4 ww = w4[i];
+            const float wx[4] = {ww.x, ww.y, ww.z, ww.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float kv = kx[e] * vv;
+              const float seen = fmaf(u[4 * i + e], kv, s[4 * i + e]);
+              if (e & 1) o1 = fmaf(seen, qx[e], o1); else o0 = fmaf(seen, qx[e], o0);
+              s[4 * i + e] = fmaf(wx[e], s[4 * i + e], kv);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              s[4 * i + e] = fmaf(decay, s[4 * i + e], kx[e] * vv);
+              if (e & 1) o1 = fmaf(s[4 * i + e], qx[e], o1); else o0 = fmaf(s[4 * i + e], qx[e], o0);
+            }
+          }
+        }
+        part[(tok * W + warp) * 32 + lane] = o0 + o1;
+      }
+      if (W > 1) asm volatile("bar.sync 1, %0;" ::"r"(W * 32) : "memory"); else __syncwarp();
+      for (int tok = warp; tok < nt; tok += W) {
+        float o = 0.f;
+        for (int w = 0; w < W; ++w) o += part[(tok * W + w) * 32 + lane];
+        if (col_ok) a.out[((size_t)(t0 + tok) * H + h) * dv + col] = o;
+      }
+    }
+    __syncthreads();
+  }
+  if (loader) return;
+#pragma unroll
+  for (int i = 0; i < RPT; ++i)
+    if (r0 + i < d && col_ok) S[(size_t)(r0 + i) * dv + col] = s[i];
+}
+
+// ------------------------------------------------------------------- token shift
+// A CTA per token. The CTA of a request's first token of the step is the only one that touches
+// the request's state: each of its threads reads its columns of the previous h there and then
+// writes the step's last h over them.
+template <typename T>
+__global__ void token_shift_mix_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ mu, int num_mixes,
+                                       float* __restrict__ state, int state_stride, const int* __restrict__ cu_q,
+                                       const int* __restrict__ state_slots, int num_seqs, int num_tokens, int C,
+                                       T* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  int lo = 0, hi = num_seqs - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu_q[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  const int start = cu_q[lo], end = cu_q[lo + 1];
+  if (t >= end) return;                          // a row that belongs to no request
+  float* st = state + (size_t)state_slots[lo] * state_stride;
+  const T* cur_row = x + (size_t)t * x_stride;
+  const T* last_row = x + (size_t)(end - 1) * x_stride;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    const float cur = to_float(cur_row[c]);
+    float prev;
+    if (t > start) {
+      prev = to_float(x[(size_t)(t - 1) * x_stride + c]);
+    } else {
+      prev = st[c];
+      st[c] = to_float(last_row[c]);
+    }
+    const float diff = prev - cur;
+    for (int m = 0; m < num_mixes; ++m)
+      out[((size_t)m * num_tokens + t) * C + c] = from_float<T>(fmaf(diff, to_float(mu[(size_t)m * C + c]), cur));
+  }
+}
+
+}  // namespace ts
+
+using namespace ts;
+
+template <typename K>
+static int lin_allow_smem(K kern, size_t smem, size_t& allowed) {
+  if (smem <= 48 * 1024 || smem <= allowed) return 0;
+  const int e = (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e == 0) allowed = smem;
+  return e;
+}
+
+template <typename T, int MODE>
+static int launch_linear(const LinScanArgs& a, dim3 grid, cudaStream_t stream) {
+  const int dpad = a.W * LIN_RPT;
+  const int narr = MODE == MODE_BONUS ? 3 : 2;
+  const size_t smem = sizeof(float) * (2 * (size_t)a.CH * (narr * dpad + 32) + (size_t)a.CH * a.W * 32);
+  auto kern = linear_scan_kernel<T, MODE>;
+  static size_t allowed = 0;
+  if (int e = lin_allow_smem(kern, smem, allowed)) return e;
+  return launch(kern, grid, (a.W + LIN_LOADER_WARPS) * 32, smem, stream, a);
+}
+
+// mode 0: bonus read-out with a decay per key channel and token; mode 1: constant decay per head, SiLU on q, k, v.
+extern "C" int ts_linear_scan(int mode, const void* q, int q_stride, const void* k, int k_stride, const void* v,
+                              int v_stride, const float* w_pre, int w_stride, const float* w_bias, const float* bonus,
+                              const float* decay, float* state, int state_stride, const int* cu_q,
+                              const int* state_slots, int num_seqs, int heads, int d, int dv, float* out, int dtype,
+                              cudaStream_t stream) {
+  if (num_seqs <= 0) return 0;
+  if (d <= 0 || dv <= 0 || d > LIN_MAX_KEY_DIM) return TS_ERR_UNSUPPORTED;
+  if (mode == MODE_BONUS ? (!w_pre || !w_bias || !bonus) : (mode != MODE_DECAY || !decay)) return TS_ERR_BAD_ARGUMENT;
+  if (dtype != TS_DTYPE_F32 && dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
+  LinScanArgs a;
+  a.q = q; a.q_stride = q_stride; a.k = k; a.k_stride = k_stride; a.v = v; a.v_stride = v_stride;
+  a.w_pre = w_pre; a.w_stride = w_stride; a.w_bias = w_bias; a.bonus = bonus; a.decay = decay;
+  a.state = state; a.state_stride = state_stride; a.cu_q = cu_q; a.state_slots = state_slots;
+  a.H = heads; a.d = d; a.dv = dv; a.out = out;
+  a.W = (d + LIN_RPT - 1) / LIN_RPT;
+  a.CH = a.W * LIN_RPT <= 128 ? 16 : 8;
+  dim3 grid(num_seqs, heads, (dv + 31) / 32);
+  if (mode == MODE_BONUS)
+    return dtype == TS_DTYPE_F32 ? launch_linear<float, MODE_BONUS>(a, grid, stream) : launch_linear<bf16, MODE_BONUS>(a, grid, stream);
+  return dtype == TS_DTYPE_F32 ? launch_linear<float, MODE_DECAY>(a, grid, stream) : launch_linear<bf16, MODE_DECAY>(a, grid, stream);
+}
+
+extern "C" int ts_token_shift_mix(const void* x, int x_stride, const void* mu, int num_mixes, float* state,
+                                  int state_stride, const int* cu_q, const int* state_slots, int num_seqs,
+                                  int num_tokens, int channels, void* out, int dtype, cudaStream_t stream) {
+  if (num_tokens <= 0 || num_seqs <= 0) return 0;
+  if (num_mixes <= 0 || channels <= 0) return TS_ERR_BAD_ARGUMENT;
+  const int threads = 128;
+  int by = (channels + threads - 1) / threads;
+  if (by > 64) by = 64;
+  dim3 grid(num_tokens, by);
+  if (dtype == TS_DTYPE_F32)
+    return launch(token_shift_mix_kernel<float>, grid, threads, 0, stream, (const float*)x, x_stride, (const float*)mu,
+                  num_mixes, state, state_stride, cu_q, state_slots, num_seqs, num_tokens, channels, (float*)out);
+  if (dtype == TS_DTYPE_BF16)
+    return launch(token_shift_mix_kernel<bf16>, grid, threads, 0, stream, (const bf16*)x, x_stride, (const bf16*)mu,
+                  num_mixes, state, state_stride, cu_q, state_slots, num_seqs, num_tokens, channels, (bf16*)out);
+  return TS_ERR_BAD_ARGUMENT;
+}

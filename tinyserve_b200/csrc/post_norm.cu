@@ -1,7 +1,8 @@
 // Residual sum with a norm on the sub-layer's output, fused with the norm in front of the next
 // sub-layer. For a row x of the 32-bit stream and the pending sub-layer output d (model dtype):
 //
-//   y   = d / sqrt(mean(d^2) + eps_post) * gain(post_weight) * layer_scale      (when a post norm is pending)
+//   y   = d / sqrt(mean(d^2) + eps_post) * gain(post_weight) * layer_scale * m  (when a post norm is pending;
+//                                                                                  m a constant multiplier)
 //   x  <- x + y                                                                   (written back unless `rows`)
 //   out = x / sqrt(mean(x^2) + eps) * gain(weight)
 //
@@ -14,31 +15,6 @@
 
 namespace ts {
 
-template <typename T> struct Quad;
-template <> struct Quad<float> {
-  static __device__ __forceinline__ void load(const float* p, float* f) {
-    const float4 v = *reinterpret_cast<const float4*>(p);
-    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
-  }
-  static __device__ __forceinline__ void store(float* p, const float* f) {
-    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
-  }
-};
-template <> struct Quad<bf16> {
-  static __device__ __forceinline__ void load(const bf16* p, float* f) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(p);
-    f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xffff0000u);
-    f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xffff0000u);
-  }
-  static __device__ __forceinline__ void store(bf16* p, const float* f) {
-    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
-    uint2 pk;
-    pk.x = *reinterpret_cast<uint32_t*>(&a);
-    pk.y = *reinterpret_cast<uint32_t*>(&b);
-    *reinterpret_cast<uint2*>(p) = pk;
-  }
-};
-
 struct PostNormArgs {
   float* resid;
   const void* delta;        // may be null: nothing pending
@@ -49,6 +25,7 @@ struct PostNormArgs {
   const int* rows;
   int num_rows, hidden;
   float post_eps, eps;
+  float post_mult;          // a constant on the normed pending output
   int post_offset, offset;  // 1: the gain is 1 + weight
 };
 
@@ -90,7 +67,7 @@ __global__ void post_norm_add_rms_norm_kernel(PostNormArgs a) {
         float g[VEC];
         if constexpr (VEC == 4) Quad<T>::load(pw + i, g); else g[0] = to_float(pw[i]);
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) y[e] = xs[i + e] * post_rstd * (a.post_offset ? 1.f + g[e] : g[e]);
+        for (int e = 0; e < VEC; ++e) y[e] = xs[i + e] * post_rstd * (a.post_offset ? 1.f + g[e] : g[e]) * a.post_mult;
       } else {
         if constexpr (VEC == 4) Quad<T>::load(d + i, y); else y[0] = to_float(d[i]);
       }
@@ -126,8 +103,8 @@ __global__ void post_norm_add_rms_norm_kernel(PostNormArgs a) {
 using namespace ts;
 
 extern "C" int ts_post_norm_add_rms_norm(float* resid, const void* delta, const void* post_weight, const void* layer_scale,
-                                         float post_eps, int post_offset, const void* weight, int offset, float eps,
-                                         void* out, const int* rows, int num_rows, int hidden, int dtype,
+                                         float post_eps, int post_offset, float post_mult, const void* weight, int offset,
+                                         float eps, void* out, const int* rows, int num_rows, int hidden, int dtype,
                                          cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   if (hidden <= 0 || hidden > 12288 || !weight || !out || !resid) return TS_ERR_BAD_ARGUMENT;
@@ -136,7 +113,7 @@ extern "C" int ts_post_norm_add_rms_norm(float* resid, const void* delta, const 
   PostNormArgs a;
   a.resid = resid; a.delta = delta; a.post_weight = post_weight; a.layer_scale = layer_scale; a.weight = weight;
   a.out = out; a.rows = rows; a.num_rows = num_rows; a.hidden = hidden; a.post_eps = post_eps; a.eps = eps;
-  a.post_offset = post_offset; a.offset = offset;
+  a.post_offset = post_offset; a.offset = offset; a.post_mult = post_mult;
   const size_t smem = sizeof(float) * (size_t)hidden;
   const bool aligned = hidden % 4 == 0 &&
       (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)post_weight | (uintptr_t)layer_scale | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;

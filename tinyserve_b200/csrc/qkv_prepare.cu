@@ -3,8 +3,9 @@
 // rotation of the first `rotary_dim` elements (element i pairs with i + rotary_dim / 2), then
 // queries go to q_out [T, heads, d], keys to k_cache [pages, kv_heads, page_size, d] and values,
 // unchanged, to v_cache [pages, kv_heads, page_size, dv] at the token's slot. q, k and v are read
-// from rows with strides of their own, so they may be parts of one merged projection. All
-// arithmetic is 32-bit and the result is rounded once.
+// from rows with strides of their own, so they may be parts of one merged projection. Optional
+// biases (one value per projection row) are added first. All arithmetic is 32-bit and the result
+// is rounded once.
 #define TS_PDL_CLASS PDL_ELEMENTWISE
 #include "common.cuh"
 
@@ -39,11 +40,13 @@ template <> struct Pair<bf16> {
 // written with its rotation partner taken from that row. Heads of an even size at an aligned
 // address move two elements per access.
 template <typename T>
-__device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const T* __restrict__ w, float eps,
+__device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const T* __restrict__ bias,
+                                                 const T* __restrict__ w, float eps,
                                                  const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                  int rotary_dim, int d, T* __restrict__ dst, int lane,
                                                  float* __restrict__ row) {
-  const bool pairs = (d & 1) == 0 && ((((uintptr_t)x) | ((uintptr_t)dst) | ((uintptr_t)w)) & Pair<T>::MASK) == 0;
+  const bool pairs = (d & 1) == 0 &&
+      ((((uintptr_t)x) | ((uintptr_t)dst) | ((uintptr_t)w) | ((uintptr_t)bias)) & Pair<T>::MASK) == 0;
   const int half = rotary_dim >> 1;
   float ss = 0.f;
   if (pairs) {
@@ -59,6 +62,12 @@ __device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const 
       s0[j] = s1[j] = 0.f;
       if (i < d) {
         Pair<T>::load(x + i, a[j], b[j]);
+        if (bias) {
+          float ba, bb;
+          Pair<T>::load(bias + i, ba, bb);
+          a[j] += ba;
+          b[j] += bb;
+        }
         if (w) Pair<T>::load(w + i, wa[j], wb[j]);
         if (i < rotary_dim) {
           const int f = i < half ? i : i - half;
@@ -102,7 +111,7 @@ __device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const 
     return;
   }
   for (int i = lane; i < d; i += 32) {
-    const float v = to_float(x[i]);
+    const float v = to_float(x[i]) + (bias ? to_float(bias[i]) : 0.f);
     row[i] = w ? v * to_float(w[i]) : v;
     ss = fmaf(v, v, ss);
   }
@@ -122,7 +131,8 @@ __device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const 
 
 template <typename T>
 __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, int q_stride, const T* __restrict__ k_in, int k_stride,
-                                   const T* __restrict__ v_in, int v_stride, const T* __restrict__ q_w,
+                                   const T* __restrict__ v_in, int v_stride, const T* __restrict__ q_b,
+                                   const T* __restrict__ k_b, const T* __restrict__ v_b, const T* __restrict__ q_w,
                                    const T* __restrict__ k_w, float eps, const float* __restrict__ cos_tab,
                                    const float* __restrict__ sin_tab, int rotary_dim, const int* __restrict__ slots,
                                    T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int num_tokens,
@@ -139,7 +149,7 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, int q_stride, con
   const float* cos_t = rotary_dim ? cos_tab + (size_t)t * (rotary_dim >> 1) : nullptr;
   const float* sin_t = rotary_dim ? sin_tab + (size_t)t * (rotary_dim >> 1) : nullptr;
   if (job < heads) {
-    norm_rotate_head(q_in + (size_t)t * q_stride + job * d, q_w, eps, cos_t, sin_t, rotary_dim, d,
+    norm_rotate_head(q_in + (size_t)t * q_stride + job * d, q_b ? q_b + job * d : nullptr, q_w, eps, cos_t, sin_t, rotary_dim, d,
                      q_out + ((size_t)t * heads + job) * d, lane, row);
     return;
   }
@@ -147,19 +157,28 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, int q_stride, con
   const int page = slot / page_size, off = slot - page * page_size;
   if (job < heads + kv_heads) {
     const int g = job - heads;
-    norm_rotate_head(k_in + (size_t)t * k_stride + g * d, k_w, eps, cos_t, sin_t, rotary_dim, d,
+    norm_rotate_head(k_in + (size_t)t * k_stride + g * d, k_b ? k_b + g * d : nullptr, k_w, eps, cos_t, sin_t, rotary_dim, d,
                      k_cache + (((size_t)page * kv_heads + g) * page_size + off) * d, lane, row);
     return;
   }
   const int g = job - heads - kv_heads;
   const T* src = v_in + (size_t)t * v_stride + g * dv;
   T* dst = v_cache + (((size_t)page * kv_heads + g) * page_size + off) * dv;
-  if ((dv & 1) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & Pair<T>::MASK) == 0) {
+  const T* vb = v_b ? v_b + g * dv : nullptr;
+  if ((dv & 1) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst) | ((uintptr_t)vb)) & Pair<T>::MASK) == 0) {
     for (int i = 2 * lane; i < dv; i += 64) {
       float a, b;
       Pair<T>::load(src + i, a, b);
+      if (vb) {
+        float ba, bb;
+        Pair<T>::load(vb + i, ba, bb);
+        a += ba;
+        b += bb;
+      }
       Pair<T>::store(dst + i, a, b);
     }
+  } else if (vb) {
+    for (int i = lane; i < dv; i += 32) dst[i] = from_float<T>(to_float(src[i]) + to_float(vb[i]));
   } else {
     for (int i = lane; i < dv; i += 32) dst[i] = src[i];
   }
@@ -170,7 +189,7 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, int q_stride, con
 using namespace ts;
 
 extern "C" int ts_qkv_prepare(const void* q_in, int q_stride, const void* k_in, int k_stride, const void* v_in,
-                              int v_stride, const void* q_w, const void* k_w, float eps, const float* cos_tab,
+                              int v_stride, const void* q_b, const void* k_b, const void* v_b, const void* q_w, const void* k_w, float eps, const float* cos_tab,
                               const float* sin_tab, int rotary_dim, const int* slots, void* k_cache, void* v_cache,
                               int page_size, int num_tokens, int heads, int kv_heads, int d, int dv, void* q_out,
                               int dtype, cudaStream_t stream) {
@@ -183,12 +202,12 @@ extern "C" int ts_qkv_prepare(const void* q_in, int q_stride, const void* k_in, 
   const int blocks = (int)((warps * 32 + threads - 1) / threads);
   if (dtype == TS_DTYPE_F32)
     return launch(qkv_prepare_kernel<float>, blocks, threads, 0, stream, (const float*)q_in, q_stride, (const float*)k_in,
-                  k_stride, (const float*)v_in, v_stride, (const float*)q_w, (const float*)k_w, eps, cos_tab, sin_tab,
+                  k_stride, (const float*)v_in, v_stride, (const float*)q_b, (const float*)k_b, (const float*)v_b, (const float*)q_w, (const float*)k_w, eps, cos_tab, sin_tab,
                   rotary_dim, slots, (float*)k_cache, (float*)v_cache, page_size, num_tokens, heads, kv_heads, d, dv,
                   (float*)q_out);
   if (dtype == TS_DTYPE_BF16)
     return launch(qkv_prepare_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)q_in, q_stride, (const bf16*)k_in,
-                  k_stride, (const bf16*)v_in, v_stride, (const bf16*)q_w, (const bf16*)k_w, eps, cos_tab, sin_tab,
+                  k_stride, (const bf16*)v_in, v_stride, (const bf16*)q_b, (const bf16*)k_b, (const bf16*)v_b, (const bf16*)q_w, (const bf16*)k_w, eps, cos_tab, sin_tab,
                   rotary_dim, slots, (bf16*)k_cache, (bf16*)v_cache, page_size, num_tokens, heads, kv_heads, d, dv,
                   (bf16*)q_out);
   return TS_ERR_BAD_ARGUMENT;

@@ -193,8 +193,9 @@ __global__ void mlstm_scan_kernel(const T* __restrict__ qkv, int stride, int q_o
 // beta, 1/|k|, q_scale/|q|.
 template <int RPT>
 __global__ void delta_scan_kernel(const float* __restrict__ qkv, int stride, int q_off, int k_off, int v_off,
-                                  const float* __restrict__ a, const float* __restrict__ dt_bias,
-                                  const float* __restrict__ a_log, const float* __restrict__ beta_pre,
+                                  const float* __restrict__ a, int a_stride, int a_per_head,
+                                  const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                  const float* __restrict__ beta_pre, int beta_stride,
                                   float q_scale, float* __restrict__ state, int state_stride,
                                   const int* __restrict__ cu_q, const int* __restrict__ state_slots, int H, int G,
                                   int d, int dv, float* __restrict__ out, int W, int CH) {
@@ -233,7 +234,8 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, int stride, int
         const float* row = qkv + (size_t)(t0 + tok) * stride;
         qv[u] = ok ? row[q_off + g * d + r] : 0.f;
         kv[u] = ok ? row[k_off + g * d + r] : 0.f;
-        av[u] = ok ? a[((size_t)(t0 + tok) * H + h) * d + r] + dt_bias[h * d + r] : -INFINITY;
+        const int ac = a_per_head ? h : h * d + r;   // one step size per head, or per head and key channel
+        av[u] = ok ? a[(size_t)(t0 + tok) * a_stride + ac] + dt_bias[ac] : -INFINITY;
       }
 #pragma unroll
       for (int u = 0; u < SCAN_LOADS; ++u) {
@@ -261,7 +263,7 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, int stride, int
       qq = warp_sum(qq);
       kk = warp_sum(kk);
       if (lane == 0) {
-        const float z = beta_pre[(size_t)(t0 + tok) * H + h];
+        const float z = beta_pre[(size_t)(t0 + tok) * beta_stride + h];
         t_s[4 * tok] = 1.f / (1.f + expf(-z));
         t_s[4 * tok + 1] = rsqrtf(kk + 1e-6f);
         t_s[4 * tok + 2] = rsqrtf(qq + 1e-6f) * q_scale;
@@ -465,21 +467,23 @@ extern "C" int ts_mlstm_scan(const void* qkv, int stride, int q_off, int k_off, 
 
 template <int RPT>
 static int launch_delta(const ScanShape& sh, dim3 grid, cudaStream_t stream, const float* qkv, int stride, int q_off,
-                        int k_off, int v_off, const float* a, const float* dt_bias, const float* a_log,
-                        const float* beta_pre, float q_scale, float* state, int state_stride, const int* cu_q,
+                        int k_off, int v_off, const float* a, int a_stride, int a_per_head, const float* dt_bias,
+                        const float* a_log, const float* beta_pre, int beta_stride, float q_scale, float* state,
+                        int state_stride, const int* cu_q,
                         const int* state_slots, int heads, int kv_heads, int d, int dv, float* out) {
   const int dpad = sh.warps * RPT;
   const size_t smem = sizeof(float) * (2 * (size_t)sh.chunk * (3 * dpad + 32 + 4) + (2 + (size_t)sh.chunk) * sh.warps * 32);
   auto kern = delta_scan_kernel<RPT>;
   static size_t allowed = 0;
   if (int e = allow_smem(kern, smem, allowed)) return e;
-  return launch(kern, grid, (sh.warps + SCAN_LOADER_WARPS) * 32, smem, stream, qkv, stride, q_off, k_off, v_off, a, dt_bias,
-                a_log, beta_pre, q_scale, state, state_stride, cu_q, state_slots, heads, kv_heads, d, dv, out, sh.warps,
+  return launch(kern, grid, (sh.warps + SCAN_LOADER_WARPS) * 32, smem, stream, qkv, stride, q_off, k_off, v_off, a, a_stride,
+                a_per_head, dt_bias, a_log, beta_pre, beta_stride, q_scale, state, state_stride, cu_q, state_slots, heads, kv_heads, d, dv, out, sh.warps,
                 sh.chunk);
 }
 
 extern "C" int ts_delta_scan(const float* qkv, int stride, int q_off, int k_off, int v_off, const float* a,
-                             const float* dt_bias, const float* a_log, const float* beta_pre, float q_scale,
+                             int a_stride, int a_per_head, const float* dt_bias, const float* a_log,
+                             const float* beta_pre, int beta_stride, float q_scale,
                              float* state, int state_stride, const int* cu_q, const int* state_slots, int num_seqs,
                              int heads, int kv_heads, int d, int dv, float* out, cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
@@ -488,7 +492,8 @@ extern "C" int ts_delta_scan(const float* qkv, int stride, int q_off, int k_off,
   const ScanShape sh = scan_shape(d);
   dim3 grid(num_seqs, heads, (dv + 31) / 32);
 #define TS_DELTA_CASE(RPT_)                                                                                        \
-  return launch_delta<RPT_>(sh, grid, stream, qkv, stride, q_off, k_off, v_off, a, dt_bias, a_log, beta_pre, q_scale, \
+  return launch_delta<RPT_>(sh, grid, stream, qkv, stride, q_off, k_off, v_off, a, a_stride, a_per_head, dt_bias, a_log, \
+                            beta_pre, beta_stride, q_scale, \
                             state, state_stride, cu_q, state_slots, heads, kv_heads, d, dv, out)
   if (sh.rpt == 32) { TS_DELTA_CASE(32); }
   if (sh.rpt == 64) { TS_DELTA_CASE(64); }

@@ -38,8 +38,8 @@ class Replayer:
 
     @classmethod
     def from_folder(cls, model_dir: str | Path, dtype: torch.dtype, max_tokens: int,
-                    page_size: int = DEFAULT_PAGE_SIZE, device: str = "cuda") -> "Replayer":
-        return cls(DecoderModel.from_folder(model_dir, dtype, device), max_tokens, page_size)
+                    page_size: int = DEFAULT_PAGE_SIZE, device: str = "cuda", max_live: int = 64) -> "Replayer":
+        return cls(DecoderModel.from_folder(model_dir, dtype, device), max_tokens, page_size, max_live)
 
     def run_step(self, entries: Sequence[tuple[str, Sequence[int], Sequence[int]]],
                  end: Sequence[str] = ()) -> torch.Tensor | None:

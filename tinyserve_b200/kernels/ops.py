@@ -34,18 +34,25 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
     "ts_qk_norm_rope_write": [_vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ts_paged_attention_simt": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
-                                _f, _i, _i, _vp, _vp, _vp, _i, _i, _vp],
+                                _f, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp],
     "ts_hc_mix_norm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp],
     "ts_hc_collapse": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "ts_act_mul": [_vp, _vp, _i, _i, _i, _f, _i, _vp],
+    "ts_act_mul": [_vp, _vp, _vp, _i, _i, _i, _f, _i, _vp],
+    "ts_act_mul_gather": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _i, _i, _i, _i, _vp],
+    "ts_embed_pos_norm": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _i, _vp],
+    "ts_stream_sum": [_vp, _vp, _vp, _vp, _vp, _f, _f, _f, _f, _i, _vp, _f, _vp, _i, _i, _i, _vp],
+    "ts_add_bias": [_vp, _vp, _i, _i, _i, _vp],
+    "ts_tanh": [_vp, _c.c_size_t, _i, _vp],
+    "ts_linear_scan": [_i, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp],
+    "ts_token_shift_mix": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _vp, _i, _vp],
     "ts_softcap": [_vp, _c.c_size_t, _f, _vp],
-    "ts_head_norm_gate": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
-    "ts_post_norm_add_rms_norm": [_vp, _vp, _vp, _vp, _f, _i, _vp, _i, _f, _vp, _vp, _i, _i, _i, _vp],
+    "ts_head_norm_gate": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
+    "ts_post_norm_add_rms_norm": [_vp, _vp, _vp, _vp, _f, _i, _f, _vp, _i, _f, _vp, _vp, _i, _i, _i, _vp],
     "ts_mlstm_scan": [_vp, _i, _i, _i, _i, _vp, _vp, _f, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp],
-    "ts_delta_scan": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
+    "ts_delta_scan": [_vp, _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ts_causal_conv_silu": [_vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp],
-    "ts_qkv_prepare": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _f, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                       _vp, _i, _vp],
+    "ts_qkv_prepare": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i,
+                       _i, _i, _vp, _i, _vp],
     "ts_prefill_attention_mma": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "ts_decode_attention_mma": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp,
                                 _vp, _vp],
@@ -225,9 +232,10 @@ def add_rms_norm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.
 
 def post_norm_add_rms_norm(resid: torch.Tensor, delta: torch.Tensor | None, post_weight: torch.Tensor | None,
                            layer_scale: torch.Tensor | None, post_eps: float, post_offset: bool, weight: torch.Tensor,
-                           offset: bool, eps: float, out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
+                           offset: bool, eps: float, out: torch.Tensor, rows: torch.Tensor | None = None,
+                           post_mult: float = 1.0) -> None:
     """The residual sum with a norm on the pending sub-layer output, and the next norm, in one pass,
-    all in 32-bit: ``y = delta / sqrt(mean(delta^2) + post_eps) * gain(post_weight) * layer_scale``
+    all in 32-bit: ``y = post_mult * delta / sqrt(mean(delta^2) + post_eps) * gain(post_weight) * layer_scale``
     (``post_weight`` / ``layer_scale`` ``None``: that factor is left out), ``x = resid + y``,
     ``out = dt(x / sqrt(mean(x^2) + eps) * gain(weight))`` with ``gain(w) = 1 + w`` when the matching
     ``offset`` flag is set, else ``w``. Without ``rows`` the sum is written back to ``resid``; with
@@ -244,7 +252,7 @@ def post_norm_add_rms_norm(resid: torch.Tensor, delta: torch.Tensor | None, post
         raise KernelError("post_norm_add_rms_norm: out must have one row per row of resid, or per entry of rows")
     _check(_fn("ts_post_norm_add_rms_norm")(
         _dev(resid, "resid", torch.float32), _opt(delta, "delta", dt), _opt(post_weight, "post_weight", dt),
-        _opt(layer_scale, "layer_scale", dt), float(post_eps), int(bool(post_offset)), _dev(weight, "weight", dt),
+        _opt(layer_scale, "layer_scale", dt), float(post_eps), int(bool(post_offset)), float(post_mult), _dev(weight, "weight", dt),
         int(bool(offset)), float(eps), _dev(out, "out"), _opt(rows, "rows", torch.int32), n, h, _code(dt), _stream()),
         "post_norm_add_rms_norm")
 
@@ -405,7 +413,7 @@ def choose_splits(ctas: int, slots: int, most: int, cluster: bool = False) -> in
 
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
                     block_tables: torch.Tensor, ctx: Any, scale: float, window: int, out: torch.Tensor,
-                    sinks: torch.Tensor | None = None) -> None:
+                    sinks: torch.Tensor | None = None, keep_first: int = 0) -> None:
     """Causal attention of this step's queries over each request's cached keys and values.
 
     ``q`` ``[T, Hq, D]`` dt; key cache ``[pages, Hkv, page_size, D]`` dt, value cache the same
@@ -413,7 +421,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     ``cu_query_lens``, ``context_lens_dev``, the lists of decoding and prefilling requests and the
     step's maxima. ``window`` 0 means all earlier positions. ``sinks`` (float32 ``[Hq]``,
     optional): a logit per head that joins the softmax's denominator, unscaled, without a value.
-    ``out`` ``[T, Hq * Dv]`` dt."""
+    ``keep_first`` (with a window): positions below it stay visible to every later query, whatever
+    the window. ``out`` ``[T, Hq * Dv]`` dt."""
     t, hq, d = q.shape
     hkv = k_cache.shape[1]
     dv = v_cache.shape[3]
@@ -428,7 +437,11 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
               and k_cache.shape[0] * hkv * page_size < 2 ** 31)
     # sink logits are known to the tcgen05 prompt kernel, the TMA decode kernel and the CUDA-core
     # kernels; a value head size of its own and odd head sizes to the CUDA-core kernels only
-    simt_only = dv != d or d % 16 != 0 or (sinks is not None and not (tma_ok and PREFILL_ATTENTION == "tcgen05"))
+    keep_first = int(keep_first) if window > 0 else 0
+    if keep_first < 0:
+        raise KernelError("paged_attention: keep_first must not be negative")
+    simt_only = (dv != d or d % 16 != 0 or keep_first > 0
+                 or (sinks is not None and not (tma_ok and PREFILL_ATTENTION == "tcgen05")))
     if d > 256 or dv > 256:
         raise KernelError(f"paged_attention: head sizes {d}/{dv} must be at most 256")
     if block_tables.dim() != 2 or block_tables.shape[0] != ctx.num_seqs:
@@ -439,7 +452,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     num_prefill = ctx.num_prefill
     if simt_only:
         # the CUDA-core kernels know sink logits, a value head size of its own and odd head sizes
-        _paged_attention_simt(q, k_cache, v_cache, page_size, block_tables, ctx, scale, window, out, sinks, num_prefill)
+        _paged_attention_simt(q, k_cache, v_cache, page_size, block_tables, ctx, scale, window, out, sinks, num_prefill,
+                              keep_first)
         return
     if num_prefill and dt == torch.bfloat16 and d <= 128:
         # prefill rows on the tensor cores; the decode rows follow below
@@ -507,7 +521,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 
 def _paged_attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
                           block_tables: torch.Tensor, ctx: Any, scale: float, window: int, out: torch.Tensor,
-                          sinks: torch.Tensor | None, num_prefill: int) -> None:
+                          sinks: torch.Tensor | None, num_prefill: int, keep_first: int = 0) -> None:
     t, hq, d = q.shape
     hkv, dv, dt = k_cache.shape[1], v_cache.shape[3], q.dtype
     splits, part_acc, part_ml = 1, None, None
@@ -525,7 +539,7 @@ def _paged_attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
         _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), num_prefill, ctx.max_query_len,
         hq, hkv, d, page_size, float(scale), int(window), splits,
         _opt(part_acc, "part_acc"), _opt(part_ml, "part_ml"), _opt(sinks, "sinks", torch.float32), dv,
-        _code(dt), _stream()), "paged_attention",
+        int(keep_first), _code(dt), _stream()), "paged_attention",
         kernels=(1 if num_prefill else 0) + (1 if ctx.num_decode else 0))
 
 
@@ -1100,8 +1114,10 @@ def hc_collapse(lanes: torch.Tensor, fresh: torch.Tensor | None, delta: torch.Te
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
 
 
-def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str, limit: float = 0.0) -> None:
-    """``out[t, j] = dt(act(gate_up[t, j]) * gate_up[t, I + j])`` in 32-bit, rounded once;
+def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str, limit: float = 0.0,
+            bias: torch.Tensor | None = None) -> None:
+    """``out[t, j] = dt(act(gate_up[t, j]) * gate_up[t, I + j])`` in 32-bit, rounded once (with
+    ``bias [2 I]`` dt, ``bias[j]`` and ``bias[I + j]`` are added to the two factors first);
     ``activation``: "silu", "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))) or
     "clamped_swish": with ``g = min(gate, limit)`` and ``u = clamp(up, -limit, limit)`` the result is
     ``g sigmoid(1.702 g) (u + 1)``."""
@@ -1110,7 +1126,9 @@ def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str, limit: fl
         raise KernelError("act_mul: shape, dtype or activation")
     if activation == "clamped_swish" and not limit > 0:
         raise KernelError("act_mul: the clamped activation needs a positive limit")
-    _check(_fn("ts_act_mul")(_dev(gate_up, "gate_up"), _dev(out, "out"), t, inter, ACTIVATIONS[activation],
+    if bias is not None and (bias.shape != (2 * inter,) or bias.dtype != out.dtype):
+        raise KernelError("act_mul: bias must have one value per column of gate_up")
+    _check(_fn("ts_act_mul")(_dev(gate_up, "gate_up"), _opt(bias, "bias"), _dev(out, "out"), t, inter, ACTIVATIONS[activation],
                              float(limit), _code(out.dtype), _stream()), "act_mul")
 
 
@@ -1120,12 +1138,14 @@ def softcap(logits: torch.Tensor, cap: float) -> None:
 
 
 def head_norm_gate(x: torch.Tensor, weight: torch.Tensor | None, weight_per_head: bool, gate: torch.Tensor | None,
-                   normalise: bool, eps: float, out: torch.Tensor, gate_per_head: bool = False) -> None:
+                   normalise: bool, eps: float, out: torch.Tensor, gate_per_head: bool = False,
+                   gate_silu: bool = False) -> None:
     """Per (token, head) of ``x [T, H, w]`` (float32 or dt): divide by the root mean square over
     ``w`` (``normalise``), multiply by ``weight`` (``[H * w]`` when ``weight_per_head`` else ``[w]``
     shared by the heads) and by ``sigmoid(gate[t, h, :])`` (``gate`` dt, rows of ``H * w`` values,
     possibly a column slice of a wider matrix; with ``gate_per_head`` the gate has ``H`` values a row
-    and head ``h`` is multiplied by ``sigmoid(gate[t, h])``); ``out [T, H * w]`` dt."""
+    and head ``h`` is multiplied by ``sigmoid(gate[t, h])``; with ``gate_silu`` the gate's value is
+    ``z sigmoid(z)`` instead of ``sigmoid(z)``); ``out [T, H * w]`` dt."""
     t, heads, w = x.shape
     dt = out.dtype
     if out.numel() != t * heads * w or x.dtype not in (torch.float32, dt):
@@ -1140,7 +1160,7 @@ def head_norm_gate(x: torch.Tensor, weight: torch.Tensor | None, weight_per_head
     _check(_fn("ts_head_norm_gate")(
         _dev(x, "x"), int(x.dtype == torch.float32), _opt(weight, "weight", dt), w if weight_per_head else 0,
         None if gate is None else gate.data_ptr(), gate_stride, _dev(out, "out"), t, heads, w, int(bool(normalise)),
-        float(eps), int(bool(gate_per_head)), _code(dt), _stream()), "head_norm_gate")
+        float(eps), int(bool(gate_per_head)), int(bool(gate_silu)), _code(dt), _stream()), "head_norm_gate")
 
 
 # ---------------------------------------------------------------- recurrent mixers
@@ -1187,22 +1207,26 @@ def mlstm_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, gates: tor
 def delta_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, a: torch.Tensor, dt_bias: torch.Tensor,
                a_log: torch.Tensor, beta_pre: torch.Tensor, q_scale: float, state: torch.Tensor, ctx: Any,
                heads: int, kv_heads: int, d: int, dv: int, out: torch.Tensor) -> None:
-    """The gated delta rule with a decay per key channel over this step's tokens, from and to the
+    """The gated delta rule with a decay per key channel (or, when ``a`` has one column per head, one
+    decay per head: then ``dt_bias`` is ``[heads]`` too) over this step's tokens, from and to the
     state slot. ``qkv [T, *]`` float32 holds q, k (``kv_heads * d``) and v (``heads * dv``) after
     their convolutions; ``a [T, heads * d]`` float32 the step-size pre-activations, ``dt_bias
     [heads * d]``, ``a_log [heads]``, ``beta_pre [T, heads]`` float32; ``state [slots, heads * d * dv]``
     float32; ``out [T, heads, dv]`` float32. q and k are scaled to unit length inside (q also by
     ``q_scale``); head h reads q/k head ``h // (heads / kv_heads)``."""
     t = qkv.shape[0]
-    if a.shape != (t, heads * d) or beta_pre.shape != (t, heads) or tuple(out.shape) != (t, heads, dv):
+    per_head = a.shape[1] == heads and d != 1
+    if a.shape not in ((t, heads * d), (t, heads)) or beta_pre.shape != (t, heads) or tuple(out.shape) != (t, heads, dv):
         raise KernelError("delta_scan: shape mismatch")
-    if dt_bias.shape != (heads * d,) or a_log.shape != (heads,) or d > SCAN_MAX_KEY_DIM:
+    if a.stride(1) != 1 or beta_pre.stride(1) != 1 or a.dtype != torch.float32 or beta_pre.dtype != torch.float32:
+        raise KernelError("delta_scan: a and beta_pre must be float32 with unit column stride")
+    if dt_bias.shape != (a.shape[1],) or a_log.shape != (heads,) or d > SCAN_MAX_KEY_DIM:
         raise KernelError("delta_scan: parameter or key size")
     state_ptr, state_stride = _state_rows(state, heads * d * dv, "delta_scan")
     _check(_fn("ts_delta_scan")(
-        _dev(qkv, "qkv", torch.float32), qkv.shape[1], q_off, k_off, v_off, _dev(a, "a", torch.float32),
+        _dev(qkv, "qkv", torch.float32), qkv.shape[1], q_off, k_off, v_off, a.data_ptr(), a.stride(0), int(per_head),
         _dev(dt_bias, "dt_bias", torch.float32), _dev(a_log, "a_log", torch.float32),
-        _dev(beta_pre, "beta_pre", torch.float32), float(q_scale), state_ptr, state_stride,
+        beta_pre.data_ptr(), beta_pre.stride(0), float(q_scale), state_ptr, state_stride,
         _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32), _dev(ctx.state_slots, "state_slots", torch.int32),
         ctx.num_seqs, heads, kv_heads, d, dv, _dev(out, "out", torch.float32), _stream()), "delta_scan")
 
@@ -1213,21 +1237,162 @@ def causal_conv_silu(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, c
     start); afterwards the state holds the request's last ``K - 1`` inputs. ``x [T, C]`` dt, ``taps [C, K]`` dt."""
     t, c = x.shape
     k = taps.shape[1]
-    if taps.shape[0] != c or tuple(out.shape) != (t, c) or taps.dtype != x.dtype:
-        raise KernelError("causal_conv_silu: shape or dtype mismatch")
+    if taps.shape[0] != c or tuple(out.shape) != (t, c) or taps.dtype != x.dtype or not x.is_cuda or x.stride(1) != 1:
+        raise KernelError("causal_conv_silu: shape or dtype mismatch (x may be a column slice with unit column stride)")
     state_ptr, state_stride = _state_rows(state, (k - 1) * c, "causal_conv_silu")
     _check(_fn("ts_causal_conv_silu")(
-        _dev(x, "x"), c, _dev(taps, "taps"), state_ptr, state_stride,
+        x.data_ptr(), x.stride(0), _dev(taps, "taps"), state_ptr, state_stride,
         _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32), _dev(ctx.state_slots, "state_slots", torch.int32),
         ctx.num_seqs, t, c, k, _dev(out, "out", torch.float32), _code(x.dtype), _stream()), "causal_conv_silu",
         kernels=2 if k > 1 else 1)
 
 
+def linear_scan_bonus(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w_pre: torch.Tensor, w_bias: torch.Tensor,
+                      bonus: torch.Tensor, state: torch.Tensor, ctx: Any, heads: int, d: int, dv: int,
+                      out: torch.Tensor) -> None:
+    """Time mixing with a decay per key channel and a bonus for the current token, over this step's
+    tokens of every request, from and to its state slot. Per head: ``o = (S + diag(u) k v^T)^T r``,
+    then ``S <- diag(w) S + k v^T`` with ``w = exp(-exp(w_pre + w_bias))``. ``r``, ``k`` ``[T, heads * d]``
+    and ``v`` ``[T, heads * dv]`` dt with unit column stride (column slices are fine); ``w_pre``
+    ``[T, heads * d]`` float32; ``w_bias``, ``bonus`` ``[heads * d]`` float32; ``state``
+    ``[slots, heads * d * dv]`` float32; ``out [T, heads, dv]`` float32."""
+    _linear_scan(0, r, k, v, w_pre, w_bias, bonus, None, state, ctx, heads, d, dv, out)
+
+
+def linear_scan_decay(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+                      ctx: Any, heads: int, d: int, dv: int, out: torch.Tensor) -> None:
+    """Linear attention with a constant decay per head: q, k and v pass SiLU (32-bit); per head
+    ``S <- decay_h S + k v^T``, ``o = S^T q``. Shapes as for ``linear_scan_bonus``; ``decay [heads]`` float32."""
+    _linear_scan(1, q, k, v, None, None, None, decay, state, ctx, heads, d, dv, out)
+
+
+def _linear_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w_pre: torch.Tensor | None,
+                 w_bias: torch.Tensor | None, bonus: torch.Tensor | None, decay: torch.Tensor | None,
+                 state: torch.Tensor, ctx: Any, heads: int, d: int, dv: int, out: torch.Tensor) -> None:
+    t, dt = q.shape[0], q.dtype
+    for name, x, width in (("q", q, heads * d), ("k", k, heads * d), ("v", v, heads * dv)):
+        if not x.is_cuda or x.dtype != dt or x.shape != (t, width) or x.stride(1) != 1:
+            raise KernelError(f"linear_scan: {name} must be [T, {width}] {dt} with unit column stride on the device")
+    if tuple(out.shape) != (t, heads, dv) or d > SCAN_MAX_KEY_DIM:
+        raise KernelError("linear_scan: out shape or key size")
+    if mode == 0:
+        if (w_pre.shape != (t, heads * d) or w_pre.dtype != torch.float32 or w_pre.stride(1) != 1
+                or w_bias.shape != (heads * d,) or bonus.shape != (heads * d,)):
+            raise KernelError("linear_scan: decay pre-activations, their bias or the bonus")
+    elif decay.shape != (heads,):
+        raise KernelError("linear_scan: one decay per head")
+    state_ptr, state_stride = _state_rows(state, heads * d * dv, "linear_scan")
+    _check(_fn("ts_linear_scan")(
+        mode, q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+        None if w_pre is None else w_pre.data_ptr(), 0 if w_pre is None else w_pre.stride(0),
+        _opt(w_bias, "w_bias", torch.float32), _opt(bonus, "bonus", torch.float32), _opt(decay, "decay", torch.float32),
+        state_ptr, state_stride, _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
+        _dev(ctx.state_slots, "state_slots", torch.int32), ctx.num_seqs, heads, d, dv,
+        _dev(out, "out", torch.float32), _code(dt), _stream()), "linear_scan")
+
+
+def token_shift_mix(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, ctx: Any, out: torch.Tensor) -> None:
+    """``out[m, t] = x[t] + (x[t - 1] - x[t]) * mu[m]`` for every mix m, where the row before a
+    request's first token of the step comes from ``state [slots, C]`` float32 (zero at the request's
+    start); afterwards the state holds the request's last row. ``x [T, C]`` dt, ``mu [M, C]`` dt,
+    ``out [M, T, C]`` dt."""
+    t, c = x.shape
+    m = mu.shape[0]
+    if mu.shape != (m, c) or tuple(out.shape) != (m, t, c) or mu.dtype != x.dtype or out.dtype != x.dtype:
+        raise KernelError("token_shift_mix: shape or dtype mismatch")
+    state_ptr, state_stride = _state_rows(state, c, "token_shift_mix")
+    _check(_fn("ts_token_shift_mix")(
+        _dev(x, "x"), c, _dev(mu, "mu"), m, state_ptr, state_stride,
+        _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32), _dev(ctx.state_slots, "state_slots", torch.int32),
+        ctx.num_seqs, t, c, _dev(out, "out"), _code(x.dtype), _stream()), "token_shift_mix")
+
+
+# ------------------------------------------------------- around the residual stream
+def embed_pos_norm(tokens: torch.Tensor, positions: torch.Tensor | None, table: torch.Tensor,
+                   pos_table: torch.Tensor | None, norm_weight: torch.Tensor | None, eps: float, out: torch.Tensor,
+                   scale: float = 1.0) -> None:
+    """``x = float32(table[tokens[t]]) * scale (+ pos_table[positions[t]])``, then, with a norm weight,
+    ``x / sqrt(mean(x^2) + eps) * weight``; ``out [T, h]`` float32. An id or a position outside its
+    table gives a row of NaN."""
+    t, h = out.shape
+    dt = table.dtype
+    if tokens.shape != (t,) or table.shape[1] != h or (pos_table is not None and (pos_table.shape[1] != h or positions is None)):
+        raise KernelError("embed_pos_norm: shape mismatch")
+    if norm_weight is not None and norm_weight.shape != (h,):
+        raise KernelError("embed_pos_norm: norm weight size")
+    _check(_fn("ts_embed_pos_norm")(
+        _dev(tokens, "tokens", torch.int32), _opt(positions, "positions", torch.int32), _dev(table, "table"),
+        _opt(pos_table, "pos_table", dt), _opt(norm_weight, "norm_weight", dt), _dev(out, "out", torch.float32), t, h,
+        table.shape[0], 0 if pos_table is None else pos_table.shape[0], float(scale), float(eps), _code(dt), _stream()),
+        "embed_pos_norm")
+
+
+STREAM_SUM_MAX_TERMS = 4
+
+
+def stream_sum(resid: torch.Tensor, terms: Sequence[torch.Tensor], scales: Sequence[float],
+               bias: torch.Tensor | None = None, bias_scale: float = 1.0, copy: torch.Tensor | None = None) -> None:
+    """``resid <- resid + sum_i scales[i] * terms[i] (+ bias_scale * bias)`` in 32-bit; ``copy`` (dt,
+    optional) receives the new stream rounded once. ``terms [T, h]`` dt, up to four; ``bias [h]`` dt."""
+    t, h = resid.shape
+    if len(terms) != len(scales) or len(terms) > STREAM_SUM_MAX_TERMS:
+        raise KernelError(f"stream_sum: {len(terms)} terms, {len(scales)} scales (up to {STREAM_SUM_MAX_TERMS})")
+    dts = {x.dtype for x in terms} | ({bias.dtype} if bias is not None else set()) | ({copy.dtype} if copy is not None else set())
+    if len(dts) > 1:
+        raise KernelError("stream_sum: terms, bias and copy share the model dtype")
+    dt = dts.pop() if dts else torch.float32
+    for x in terms:
+        if tuple(x.shape) != (t, h):
+            raise KernelError("stream_sum: a term's shape")
+    if (bias is not None and bias.shape != (h,)) or (copy is not None and tuple(copy.shape) != (t, h)):
+        raise KernelError("stream_sum: bias or copy shape")
+    ptrs = [_dev(x, "term") for x in terms] + [None] * (STREAM_SUM_MAX_TERMS - len(terms))
+    sc = [float(x) for x in scales] + [0.0] * (STREAM_SUM_MAX_TERMS - len(scales))
+    _check(_fn("ts_stream_sum")(_dev(resid, "resid", torch.float32), *ptrs, *sc, len(terms), _opt(bias, "bias"),
+                                float(bias_scale), _opt(copy, "copy"), t, h, _code(dt), _stream()), "stream_sum")
+
+
+def add_bias(y: torch.Tensor, bias: torch.Tensor) -> None:
+    """In place: ``y[t, j] += bias[j]`` (32-bit sum, rounded once); ``y [T, n]`` dt, ``bias [n]`` dt."""
+    if y.dim() != 2 or bias.shape != (y.shape[1],) or bias.dtype != y.dtype:
+        raise KernelError("add_bias: shape or dtype mismatch")
+    _check(_fn("ts_add_bias")(_dev(y, "y"), _dev(bias, "bias"), y.shape[0], y.shape[1], _code(y.dtype), _stream()), "add_bias")
+
+
+def tanh_(x: torch.Tensor) -> None:
+    """In place: ``x <- tanh(x)`` (32-bit, rounded once)."""
+    _check(_fn("ts_tanh")(_dev(x, "x"), x.numel(), _code(x.dtype), _stream()), "tanh")
+
+
+def act_mul_gather(x: torch.Tensor, rows: torch.Tensor, table: torch.Tensor, col0: int, out: torch.Tensor,
+                   activation: str) -> None:
+    """``out[t, j] = dt(act(x[t, j]) * table[rows[t], col0 + j])``: a gate on a row looked up per token
+    (``rows`` int32 ``[T]``; a row outside the table gives NaN). ``x [T, n]`` dt with unit column stride."""
+    t, n = out.shape
+    if (x.shape != (t, n) or x.stride(1) != 1 or x.dtype != out.dtype or table.dtype != out.dtype or rows.shape != (t,)
+            or activation not in ("silu", "gelu_tanh") or not 0 <= col0 <= table.shape[1] - n):
+        raise KernelError("act_mul_gather: shape, dtype, activation or column range")
+    _check(_fn("ts_act_mul_gather")(x.data_ptr(), x.stride(0), _dev(rows, "rows", torch.int32), _dev(table, "table"),
+                                    table.shape[0], table.shape[1], int(col0), _dev(out, "out"), t, n,
+                                    ACTIVATIONS[activation], _code(out.dtype), _stream()), "act_mul_gather")
+
+
+def _bias(b: torch.Tensor | None, n: int, name: str, dt: torch.dtype) -> int | None:
+    """Address of an optional bias ``[n]`` dt (a slice of a longer vector is fine)."""
+    if b is None:
+        return None
+    if not b.is_cuda or b.dtype != dt or b.shape != (n,) or b.stride(0) != 1:
+        raise KernelError(f"{name} must be [{n}] {dt} on the device")
+    return b.data_ptr()
+
+
 def qkv_prepare(q_in: torch.Tensor, k_in: torch.Tensor | None, v_in: torch.Tensor | None, q_weight: torch.Tensor | None,
                 k_weight: torch.Tensor | None, eps: float, cos: torch.Tensor | None, sin: torch.Tensor | None,
                 rotary_dim: int, slots: torch.Tensor | None, k_cache: torch.Tensor | None, v_cache: torch.Tensor | None,
-                page_size: int, heads: int, kv_heads: int, d: int, dv: int, q_out: torch.Tensor) -> None:
-    """Per (token, head): optional RMSNorm over the head with a plain weight, rotation of the first
+                page_size: int, heads: int, kv_heads: int, d: int, dv: int, q_out: torch.Tensor,
+                q_bias: torch.Tensor | None = None, k_bias: torch.Tensor | None = None,
+                v_bias: torch.Tensor | None = None) -> None:
+    """Per (token, head): optional bias (one value per projection row, dt), optional RMSNorm over the head with a plain weight, rotation of the first
     ``rotary_dim`` elements (i pairs with i + rotary_dim / 2); queries to ``q_out [T, heads, d]``,
     keys and (unchanged) values to the caches at the tokens' slots (when ``k_in`` is given).
     ``q_in``/``k_in``/``v_in`` are 2-D dt with unit column stride (column slices of a merged
@@ -1248,6 +1413,8 @@ def qkv_prepare(q_in: torch.Tensor, k_in: torch.Tensor | None, v_in: torch.Tenso
     _check(_fn("ts_qkv_prepare")(
         q_in.data_ptr(), q_in.stride(0), None if k_in is None else k_in.data_ptr(), 0 if k_in is None else k_in.stride(0),
         None if v_in is None else v_in.data_ptr(), 0 if v_in is None else v_in.stride(0),
+        _bias(q_bias, heads * d, "q_bias", dt), _bias(k_bias if k_in is not None else None, kv_heads * d, "k_bias", dt),
+        _bias(v_bias if v_in is not None else None, kv_heads * dv, "v_bias", dt),
         _opt(q_weight, "q_weight", dt), _opt(k_weight, "k_weight", dt), float(eps),
         _opt(cos, "cos", torch.float32), _opt(sin, "sin", torch.float32), int(rotary_dim),
         _opt(slots, "slots", torch.int32), _opt(k_cache, "k_cache", dt), _opt(v_cache, "v_cache", dt), page_size, t,

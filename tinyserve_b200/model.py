@@ -80,7 +80,7 @@ class ModelParts:
             if family not in PART_FAMILIES:
                 raise ValueError(f"block {ls.block!r}: role {role!r} names the unknown family {family!r}")
             parts[role] = PART_FAMILIES[family].build(ls.parts[role].kind, **ls.parts[role].args)
-        return block_cls(parts)
+        return block_cls(parts, **dict(ls.block_args))
 
     def _check_order(self) -> None:
         for n, call in enumerate(self.spec.order):

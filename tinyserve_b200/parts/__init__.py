@@ -1,6 +1,6 @@
 """The parts layers are assembled from. Importing the package registers the built-in ones."""
 
-from . import attention, block, embedding, hyper, mlp, norm, recurrent, rope  # noqa: F401
+from . import attention, block, embedding, hyper, mlp, norm, recurrent, rope, token_input  # noqa: F401
 from .base import (
     BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
     Block, CacheNeed, FeedForward, KVCacheEntry, KVGroupContext, KVNeed, Mixer, Norm, PagedNeed, Part,

@@ -137,7 +137,9 @@ class GatedSinkAttention(Mixer):
     concatenated heads are multiplied by ``sigmoid(W_g h)`` and projected by ``W_o``. ``sink="zero"``
     fixes every head's sink logit at 0 (one is added to the denominator; no tensor); ``gate="head"``
     makes ``W_g`` ``[num_heads, hidden]``, one gate value for a whole head; ``window`` limits every
-    query to the last ``window`` positions, itself included. With
+    query to the last ``window`` positions, itself included, and ``keep_first`` (with a window) leaves
+    the first ``keep_first`` positions visible to every later query all the same; ``qkv_bias`` adds a
+    bias to q, k and v (the projection's name with ``.b`` added) before the norms. With
     ``own_kv=False`` the layer has no key/value tensors and only ever runs as a call that reads
     another call's cache. ``names`` maps the roles "q", "k", "v", "gate", "out", "q_norm",
     "k_norm", "sink" to tensor names after the prefix.
@@ -152,7 +154,11 @@ class GatedSinkAttention(Mixer):
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
                  scale: float, qk_norm: bool = True, qk_norm_eps: float = 1e-6, sink: "bool | str" = True,
                  own_kv: bool = True, names: Mapping[str, str] | None = None, window: int | None = None,
-                 gate: str = "element") -> None:
+                 gate: str = "element", keep_first: int = 0, qkv_bias: bool = False) -> None:
+        if keep_first < 0 or (keep_first and window is None):
+            raise ValueError(f"keep_first={keep_first} must not be negative and needs a window")
+        self.keep_first, self.qkv_bias = int(keep_first), bool(qkv_bias)
+        self.b_in = None
         if sink not in (True, False, "zero"):
             raise ValueError(f"sink={sink!r}: True (a learned logit per head), 'zero' (a fixed logit of 0) or False")
         if gate not in ("element", "head"):
@@ -175,8 +181,8 @@ class GatedSinkAttention(Mixer):
 
     def cache_need(self) -> "KVNeed | SplitKVNeed":
         if self.d == self.dv:
-            return KVNeed(self.groups, self.d, self.window)
-        return SplitKVNeed(self.groups, self.d, self.dv, self.window)
+            return KVNeed(self.groups, self.d, self.window, self.keep_first)
+        return SplitKVNeed(self.groups, self.d, self.dv, self.window, self.keep_first)
 
     def _widths(self) -> tuple[int, int, int, int]:
         """Rows of the q, k, v and gate products."""
@@ -192,6 +198,12 @@ class GatedSinkAttention(Mixer):
         else:
             specs = [TensorSpec(p + "qg", (q + g, h), merged_from=(p + n["q"], p + n["gate"]), merged_rows=(q, g))]
         specs.append(TensorSpec(p + n["out"], (h, self.heads * self.dv)))
+        if self.qkv_bias:
+            if self.own_kv:
+                specs.append(TensorSpec(p + "qkv.b", (q + k + v,), merged_from=tuple(p + n[r] + ".b" for r in ("q", "k", "v")),
+                                        merged_rows=(q, k, v)))
+            else:
+                specs.append(TensorSpec(p + n["q"] + ".b", (q,)))
         if self.qk_norm:
             specs.append(TensorSpec(p + n["q_norm"], (self.d,), init="one_plus_normal"))
             if self.own_kv:
@@ -204,6 +216,8 @@ class GatedSinkAttention(Mixer):
         p, n = prefix + self.prefix, self.names
         self.w_in = tensors[p + ("qkvg" if self.own_kv else "qg")]
         self.w_o = tensors[p + n["out"]]
+        if self.qkv_bias:
+            self.b_in = tensors[p + ("qkv.b" if self.own_kv else n["q"] + ".b")]
         if self.qk_norm:
             self.q_norm_w = tensors[p + n["q_norm"]]
             self.k_norm_w = tensors[p + n["k_norm"]] if self.own_kv else None
@@ -229,11 +243,14 @@ class GatedSinkAttention(Mixer):
                         None if rot is None else rot.cos, None if rot is None else rot.sin,
                         0 if rot is None else rot.rotary_dim, group.slots if writes_cache else None,
                         cache.k if writes_cache else None, cache.v if writes_cache else None, cache.page_size,
-                        self.heads, self.groups, self.d, self.dv, queries)
+                        self.heads, self.groups, self.d, self.dv, queries,
+                        q_bias=None if self.b_in is None else self.b_in[:q],
+                        k_bias=None if self.b_in is None or not writes_cache else self.b_in[q: q + k],
+                        v_bias=None if self.b_in is None or not writes_cache else self.b_in[q + k: q + k + v])
         width = self.heads * self.dv
         attn = arena.take((t, width), ctx.dtype)
         ops.paged_attention(queries, cache.k, cache.v, cache.page_size, group.block_tables, ctx, self.scale,
-                            self.window or 0, attn, sinks=self.sink)
+                            self.window or 0, attn, sinks=self.sink, keep_first=self.keep_first)
         gated = arena.take((t, width), ctx.dtype)
         ops.head_norm_gate(attn.view(t, self.heads, self.dv), None, False, proj[:, proj.shape[1] - g:], False, 0.0, gated,
                            gate_per_head=self.gate_per_head)

@@ -71,9 +71,12 @@ class CacheNeed:
 class PagedNeed(CacheNeed):
     """Memory per token, in pages. Calls whose needs compare equal share a page group (one pool
     of pages, one block table per request). ``window``: only the last ``window`` positions are
-    ever read again (pages behind it are given back early); ``None`` keeps every position."""
+    ever read again (pages behind it are given back early); ``None`` keeps every position.
+    ``keep_first``: with a window, the first positions that stay readable all the same (their pages
+    are never given back early)."""
 
     window: int | None = None
+    keep_first: int = 0
 
     def bytes_per_token(self, element_size: int) -> int:
         raise NotImplementedError
@@ -113,6 +116,7 @@ class KVNeed(PagedNeed):
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    keep_first: int = 0
 
     def bytes_per_token(self, element_size: int) -> int:
         return 2 * self.num_kv_heads * self.head_dim * element_size
@@ -135,6 +139,7 @@ class SplitKVNeed(PagedNeed):
     key_dim: int
     value_dim: int
     window: int | None = None
+    keep_first: int = 0
 
     def bytes_per_token(self, element_size: int) -> int:
         return self.num_kv_heads * (self.key_dim + self.value_dim) * element_size
@@ -270,7 +275,7 @@ class ResidualStream:
     ``delta`` enters the lanes (``parts.hyper``).
 
     A layer that norms a sub-layer's output before the residual sum leaves that norm pending too:
-    ``post`` holds ``(weight, layer_scale | None, eps, unit_offset)`` with which ``delta`` is normed
+    ``post`` holds ``(weight, layer_scale | None, eps, unit_offset, mult)`` with which ``delta`` is normed
     and scaled when the next norm folds it into the stream (``parts.norm.PostRMSNorm``)."""
 
     __slots__ = ("resid", "delta", "sumsq", "resid16", "_sumsq_buf", "_resid16_buf", "lanes", "connection", "post")
@@ -280,7 +285,7 @@ class ResidualStream:
         self.delta = delta
         self.lanes: torch.Tensor | None = None
         self.connection: tuple[torch.Tensor, torch.Tensor] | None = None
-        self.post: tuple[torch.Tensor, torch.Tensor | None, float, bool] | None = None
+        self.post: tuple[torch.Tensor, torch.Tensor | None, float, bool, float] | None = None
         self.sumsq: torch.Tensor | None = None
         self.resid16: torch.Tensor | None = None
         self._sumsq_buf: torch.Tensor | None = None
@@ -448,11 +453,21 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class TokenInput(Part):
+    """A per-layer input that depends on the token id itself, not only on the stream: ``forward(x,
+    ctx)`` gets the stream's current value ``x [T, hidden]`` in the model dtype and returns
+    ``[T, hidden]`` for the block to add."""
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Block:
     """Arranges the parts of one layer around the residual stream. A block class names the roles
     it wants filled: ``roles`` maps a role (a name of the block's own choosing, the key under which
     ``LayerSpec.parts`` gives the part) to the family the part comes from ("mixer",
-    "feed_forward" or "norm"); roles in ``optional_roles`` may be left out. The model builds the
+    "feed_forward", "norm" or "token_input"); roles in ``optional_roles`` may be left out. Constants of
+    the block itself (``LayerSpec.block_args``) reach the constructor as keyword arguments. The model builds the
     parts in the order of ``roles`` (which is also the order of their tensors) and hands them
     over as a dict. A block with a third norm, two mixers side by side or no feed-forward at all
     is another ``Block`` class and a ``register_block`` call."""
@@ -504,8 +519,9 @@ POSITION_ENCODINGS = _Registry("position encoding")
 BLOCKS = _Registry("block")
 EMBEDDINGS = _Registry("embedding")
 HEADS = _Registry("output head")
+TOKEN_INPUTS = _Registry("token input")
 # the families a block's roles may name
-PART_FAMILIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS}
+PART_FAMILIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "token_input": TOKEN_INPUTS}
 
 
 def register_mixer(name: str, factory: Callable[..., Mixer], **kw: Any) -> None:

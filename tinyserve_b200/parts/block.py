@@ -74,5 +74,55 @@ class SandwichBlock(Block):
             p["feed_forward_post_norm"].leave(stream, p["feed_forward"].forward(hn, ctx))
 
 
+class ParallelResidualBlock(Block):
+    """One norm whose output every sub-layer reads; their outputs are summed into the stream at once:
+    ``h = norm(x)``; ``x <- x + m * (a * mixer(h) + b * second_mixer(h) + feed_forward(h))``, with the
+    constants ``residual_mult`` m, ``mixer_scale`` a and ``second_mixer_scale`` b. Then, when the layer
+    has a ``token_input``, ``y = token_input(x)`` (it reads the new stream) is left pending with its
+    post norm (``token_input_post_norm``, which carries its own multiplier). The second mixer, the
+    feed-forward and the token input are optional. The sum is one kernel over the 32-bit stream; it
+    takes over the feed-forward's output bias and writes the copy of the stream that the token input
+    reads."""
+
+    roles = {"norm": "norm", "mixer": "mixer", "second_mixer": "mixer", "feed_forward": "feed_forward",
+             "token_input": "token_input", "token_input_post_norm": "norm"}
+    optional_roles = frozenset({"second_mixer", "feed_forward", "token_input", "token_input_post_norm"})
+
+    def __init__(self, parts: Mapping[str, Part], residual_mult: float = 1.0, mixer_scale: float = 1.0,
+                 second_mixer_scale: float = 1.0) -> None:
+        super().__init__(parts)
+        if ("token_input" in parts) != ("token_input_post_norm" in parts):
+            raise ValueError("a token input comes with its post norm")
+        if "token_input_post_norm" in parts and not hasattr(parts["token_input_post_norm"], "leave"):
+            raise TypeError("role 'token_input_post_norm' takes a norm that can stay pending (a 'post_rms_norm')")
+        self.mult, self.scale_a, self.scale_b = float(residual_mult), float(mixer_scale), float(second_mixer_scale)
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, caches: Mapping[str, Any], writes_cache: bool,
+                position: Any) -> None:
+        from ..kernels import ops
+
+        p = self.parts
+        ctx.arena.next_frame()
+        ctx.upcoming_weights = []
+        hn = p["norm"].forward(stream, ctx)
+        terms = [p["mixer"].forward(hn, ctx, caches.get("mixer"), writes_cache, position)]
+        scales = [self.mult * self.scale_a]
+        if "second_mixer" in p:
+            terms.append(p["second_mixer"].forward(hn, ctx, caches.get("second_mixer"), writes_cache, position))
+            scales.append(self.mult * self.scale_b)
+        bias = None
+        if "feed_forward" in p:
+            ff = p["feed_forward"]
+            bias = getattr(ff, "output_bias", None)
+            terms.append(ff.forward(hn, ctx) if bias is None else ff.forward(hn, ctx, add_output_bias=False))
+            scales.append(self.mult)
+        copy = ctx.arena.take(tuple(stream.resid.shape), ctx.dtype) if "token_input" in p else None
+        ops.stream_sum(stream.resid, terms, scales, bias=bias, bias_scale=self.mult, copy=copy)
+        stream.sumsq = None
+        if copy is not None:
+            p["token_input_post_norm"].leave(stream, p["token_input"].forward(copy, ctx))
+
+
+register_block("parallel_residual", ParallelResidualBlock)
 register_block("prenorm", PreNormBlock)
 register_block("sandwich", SandwichBlock)

@@ -35,6 +35,38 @@ class TokenEmbedding(Part):
         return out
 
 
+class PositionedEmbedding(Part):
+    """Token embedding plus a learned position row, optionally followed by an RMS norm with a plain
+    weight: ``x = table[token] * scale + positions[p]``, then ``x / sqrt(mean(x^2) + eps) * w``. One
+    kernel writes the result into the 32-bit stream. Positions count from 0 in each request; a
+    position beyond the table gives a row of NaN."""
+
+    recordable = EVERY_STEP
+
+    def __init__(self, name: str, vocab_size: int, hidden_size: int, position_name: str, max_positions: int,
+                 norm_name: str | None = None, eps: float = 1e-6, scale: float = 1.0) -> None:
+        self.name, self.vocab_size, self.hidden_size = name, int(vocab_size), int(hidden_size)
+        self.position_name, self.max_positions = position_name, int(max_positions)
+        self.norm_name, self.eps, self.scale = norm_name, float(eps), float(scale)
+        self.table = self.positions = self.norm_w = None
+
+    def tensor_specs(self, prefix: str) -> list[TensorSpec]:
+        specs = [TensorSpec(prefix + self.name, (self.vocab_size, self.hidden_size)),
+                 TensorSpec(prefix + self.position_name, (self.max_positions, self.hidden_size))]
+        if self.norm_name is not None:
+            specs.append(TensorSpec(prefix + self.norm_name, (self.hidden_size,), init="one_plus_normal"))
+        return specs
+
+    def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.table, self.positions = tensors[prefix + self.name], tensors[prefix + self.position_name]
+        self.norm_w = None if self.norm_name is None else tensors[prefix + self.norm_name]
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        out = ctx.arena.take((ctx.num_tokens, self.hidden_size), torch.float32)
+        ops.embed_pos_norm(ctx.tokens, ctx.positions, self.table, self.positions, self.norm_w, self.eps, out, self.scale)
+        return out
+
+
 class LMHead(Part):
     recordable = EVERY_STEP
 
@@ -70,4 +102,5 @@ class LMHead(Part):
 
 
 EMBEDDINGS.register("token_embedding", TokenEmbedding)
+EMBEDDINGS.register("positioned_embedding", PositionedEmbedding)
 HEADS.register("lm_head", LMHead)

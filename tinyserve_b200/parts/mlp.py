@@ -60,12 +60,17 @@ class GatedMLP(FeedForward):
     in place of ``act(gate) * up``) and of tensor names
     (``names``: role "gate" / "up" / "down" -> name after the prefix). Gate and up come from one
     product with the merged matrix, with the activation in the same kernel where the framework
-    has one for the step's shape (``ops.gemm_gated``)."""
+    has one for the step's shape (``ops.gemm_gated``). With ``bias`` every projection has a bias
+    (the projection's name with ``.b`` added): those of gate and up are added in the activation
+    kernel; the output's is ``output_bias``, which a block that sums the output into the stream
+    itself may take over (``forward(..., add_output_bias=False)``)."""
 
     recordable = EVERY_STEP
 
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "silu",
-                 names: "Mapping[str, str] | None" = None, limit: float | None = None) -> None:
+                 names: "Mapping[str, str] | None" = None, limit: float | None = None, bias: bool = False) -> None:
+        self.bias = bool(bias)
+        self.b_gate_up = self.output_bias = None
         if activation not in ops.ACTIVATIONS:
             raise ValueError(f"activation {activation!r} is not one of {sorted(ops.ACTIVATIONS)}")
         if (activation == "clamped_swish") != (limit is not None) or (limit is not None and not limit > 0):
@@ -77,24 +82,39 @@ class GatedMLP(FeedForward):
 
     def tensor_specs(self, prefix: str) -> list[TensorSpec]:
         p, h, i, n = prefix + self.prefix, self.hidden_size, self.intermediate_size, self.names
-        return [TensorSpec(p + n["gate"] + "+" + n["up"], (2 * i, h), merged_from=(p + n["gate"], p + n["up"]),
-                           merged_rows=(i, i)),
-                TensorSpec(p + n["down"], (h, i))]
+        specs = [TensorSpec(p + n["gate"] + "+" + n["up"], (2 * i, h), merged_from=(p + n["gate"], p + n["up"]),
+                            merged_rows=(i, i)),
+                 TensorSpec(p + n["down"], (h, i))]
+        if self.bias:
+            specs += [TensorSpec(p + n["gate"] + ".b+" + n["up"] + ".b", (2 * i,), merged_from=(p + n["gate"] + ".b", p + n["up"] + ".b"),
+                                 merged_rows=(i, i)),
+                      TensorSpec(p + n["down"] + ".b", (h,))]
+        return specs
 
     def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
         p, n = prefix + self.prefix, self.names
         self.w_gate_up = tensors[p + n["gate"] + "+" + n["up"]]
         self.w_down = tensors[p + n["down"]]
+        if self.bias:
+            self.b_gate_up = tensors[p + n["gate"] + ".b+" + n["up"] + ".b"]
+            self.output_bias = tensors[p + n["down"] + ".b"]
 
     def streamed_weights(self) -> list[torch.Tensor]:
         return [self.w_gate_up, self.w_down]
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx: StepContext, add_output_bias: bool = True) -> torch.Tensor:
         t = x.shape[0]
         act = ctx.arena.take((t, self.intermediate_size), ctx.dtype)
-        ops.gemm_gated(x, self.w_gate_up, act, ctx.arena, self.activation, self.limit)
+        if self.bias:
+            gate_up = ctx.arena.take((t, 2 * self.intermediate_size), ctx.dtype)
+            ops.gemm(x, self.w_gate_up, gate_up)
+            ops.act_mul(gate_up, act, self.activation, self.limit, bias=self.b_gate_up)
+        else:
+            ops.gemm_gated(x, self.w_gate_up, act, ctx.arena, self.activation, self.limit)
         out = ctx.arena.take((t, self.hidden_size), ctx.dtype)
         ops.gemm(act, self.w_down, out)
+        if self.bias and add_output_bias:
+            ops.add_bias(out, self.output_bias)
         return out
 
 

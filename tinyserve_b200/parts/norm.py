@@ -5,7 +5,8 @@ eps)``; ``y`` is cast to the model dtype and THEN multiplied by the weight (a pl
 not ``1 + w``). Here ``x`` is the 32-bit residual stream plus the pending sub-layer output,
 which the same kernel adds and writes back.
 
-Two options serve designs that norm differently: ``unit_offset`` (the weight is stored around
+Options serve designs that norm differently: ``round_once`` (the weight is applied in 32-bit too and
+the result rounded once), ``unit_offset`` (the weight is stored around
 zero and the gain is ``1 + weight``; the whole norm is then 32-bit with one rounding), and
 ``PostRMSNorm``, a norm on a sub-layer's OUTPUT with an optional per-column layer scale, which
 is left pending on the stream and applied by the next norm's kernel in the same pass as the
@@ -25,9 +26,10 @@ from .base import EVERY_STEP, LazyNormed, Norm, ResidualStream, StepContext, Ten
 class RMSNorm(Norm):
     recordable = EVERY_STEP
 
-    def __init__(self, name: str, size: int, eps: float, unit_offset: bool = False) -> None:
+    def __init__(self, name: str, size: int, eps: float, unit_offset: bool = False, round_once: bool = False) -> None:
         self.name, self.size, self.eps = name, int(size), float(eps)
         self.unit_offset = bool(unit_offset)
+        self.round_once = bool(round_once) or self.unit_offset
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self, prefix: str) -> list[TensorSpec]:
@@ -37,12 +39,13 @@ class RMSNorm(Norm):
         self.weight = tensors[prefix + self.name]
 
     def _run(self, stream: ResidualStream, out: torch.Tensor, rows: torch.Tensor | None) -> None:
-        if stream.post is None and not self.unit_offset:
+        if stream.post is None and not self.round_once:
             ops.add_rms_norm(stream.resid, stream.delta, self.weight, self.eps, out, rows=rows)
             return
-        post_w, post_scale, post_eps, post_offset = stream.post if stream.post is not None else (None, None, 0.0, False)
+        post_w, post_scale, post_eps, post_offset, post_mult = \
+            stream.post if stream.post is not None else (None, None, 0.0, False, 1.0)
         ops.post_norm_add_rms_norm(stream.resid, stream.delta, post_w, post_scale, post_eps, post_offset, self.weight,
-                                   self.unit_offset, self.eps, out, rows=rows)
+                                   self.unit_offset, self.eps, out, rows=rows, post_mult=post_mult)
 
     def forward(self, stream: ResidualStream, ctx: StepContext) -> torch.Tensor:
         out = ctx.arena.take((stream.resid.shape[0], self.size), ctx.dtype)
@@ -54,7 +57,7 @@ class RMSNorm(Norm):
         return out
 
     def lazy(self, stream: ResidualStream, ctx: StepContext) -> "torch.Tensor | LazyNormed":
-        if stream.delta is None and stream.sumsq is not None and not self.unit_offset:
+        if stream.delta is None and stream.sumsq is not None and not self.round_once:
             return LazyNormed(stream, self.weight, self.eps, lambda: self.forward(stream, ctx))
         return self.forward(stream, ctx)
 
@@ -67,14 +70,15 @@ class RMSNorm(Norm):
 
 class PostRMSNorm(Norm):
     """The norm on a sub-layer's output, with an optional layer scale (one factor per column,
-    tensor ``scale_name``): ``leave(stream, y)`` leaves ``y`` pending together with this norm, and
-    the next norm's kernel adds ``layer_scale * norm(y)`` to the stream."""
+    tensor ``scale_name``) and an optional constant ``mult``: ``leave(stream, y)`` leaves ``y`` pending
+    together with this norm, and the next norm's kernel adds ``mult * layer_scale * norm(y)`` to the stream."""
 
     recordable = EVERY_STEP
 
-    def __init__(self, name: str, size: int, eps: float, unit_offset: bool = False, scale_name: str | None = None) -> None:
+    def __init__(self, name: str, size: int, eps: float, unit_offset: bool = False, scale_name: str | None = None,
+                 mult: float = 1.0) -> None:
         self.name, self.size, self.eps = name, int(size), float(eps)
-        self.unit_offset, self.scale_name = bool(unit_offset), scale_name
+        self.unit_offset, self.scale_name, self.mult = bool(unit_offset), scale_name, float(mult)
         self.weight: torch.Tensor | None = None
         self.scale: torch.Tensor | None = None
 
@@ -92,7 +96,7 @@ class PostRMSNorm(Norm):
         if stream.delta is not None:
             raise RuntimeError("a sub-layer output is already pending on the stream")
         stream.delta = y
-        stream.post = (self.weight, self.scale, self.eps, self.unit_offset)
+        stream.post = (self.weight, self.scale, self.eps, self.unit_offset, self.mult)
         stream.sumsq = None
 
     def forward(self, stream: ResidualStream, ctx: StepContext) -> torch.Tensor:
