@@ -36,13 +36,13 @@ def add_rms_norm(resid, delta, weight, eps, out, rows=None) -> None:
 
 
 def post_norm_add_rms_norm(resid, delta, post_weight, layer_scale, post_eps, post_offset, weight, offset, eps, out,
-                           rows=None) -> None:
+                           rows=None, post_mult=1.0) -> None:
     x = resid if rows is None else resid[rows.long()]
     if delta is not None:
         y = (delta if rows is None else delta[rows.long()]).float()
         if post_weight is not None:
             g = post_weight.float()
-            y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + post_eps) * (1 + g if post_offset else g)
+            y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + post_eps) * (1 + g if post_offset else g) * post_mult
         if layer_scale is not None:
             y = y * layer_scale.float()
         x = x + y
@@ -106,7 +106,8 @@ def qk_norm_rope_write(qkv, q_out, q_weight, k_weight, eps, cos, sin, rotary_dim
     v_cache[page, :, off] = v
 
 
-def paged_attention(q, k_cache, v_cache, page_size, block_tables, ctx: Any, scale, window, out, sinks=None) -> None:
+def paged_attention(q, k_cache, v_cache, page_size, block_tables, ctx: Any, scale, window, out, sinks=None,
+                    keep_first=0) -> None:
     """Per request: gather its keys and values from the pages in position order, then plain
     causal (windowed) attention for its new tokens (upstream src/tinyserve/attention.py:62-111)."""
     t, hq, d = q.shape
@@ -122,14 +123,15 @@ def paged_attention(q, k_cache, v_cache, page_size, block_tables, ctx: Any, scal
         lo = 0
         if window:
             lo = max(0, (total - n) - window + 1)      # pages before this may be gone
-        pos = pos[lo:]
+        kept = min(int(keep_first), lo) if window else 0    # first positions that stay visible below the window
+        pos = torch.cat([pos[:kept], pos[lo:]])
         pages = block_tables[b].long()[pos // page_size]
         k = k_cache[pages, :, pos % page_size].float().repeat_interleave(group, dim=1)   # [keys, Hq, D]
         v = v_cache[pages, :, pos % page_size].float().repeat_interleave(group, dim=1)
         qpos = torch.arange(total - n, total, device=q.device)
         hidden = pos[None, :] > qpos[:, None]
         if window:
-            hidden = hidden | (pos[None, :] <= qpos[:, None] - window)
+            hidden = hidden | ((pos[None, :] <= qpos[:, None] - window) & (pos[None, :] >= int(keep_first)))
         s = torch.einsum("ihd,jhd->hij", q[r0: r0 + n].float(), k) * scale
         s = s.masked_fill(hidden, float("-inf"))
         if sinks is not None:
@@ -178,9 +180,11 @@ def hc_collapse(lanes, fresh, delta, mix_prev, out_prev, rows, out) -> None:
 
 
 # ---------------------------------------------------------------------------- gates
-def act_mul(gate_up, out, activation, limit=0.0) -> None:
+def act_mul(gate_up, out, activation, limit=0.0, bias=None) -> None:
     inter = out.shape[1]
     g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+    if bias is not None:
+        g, u = g + bias[:inter].float(), u + bias[inter:].float()
     if activation == "clamped_swish":
         g, u = g.clamp(max=limit), u.clamp(-limit, limit)
         out.copy_((g * torch.sigmoid(1.702 * g) * (u + 1)).to(out.dtype))
@@ -204,7 +208,7 @@ def softcap(logits, cap) -> None:
     logits.copy_(cap * torch.tanh(logits / cap))
 
 
-def head_norm_gate(x, weight, weight_per_head, gate, normalise, eps, out, gate_per_head=False) -> None:
+def head_norm_gate(x, weight, weight_per_head, gate, normalise, eps, out, gate_per_head=False, gate_silu=False) -> None:
     t, heads, w = x.shape
     y = x.float()
     if normalise:
@@ -212,7 +216,8 @@ def head_norm_gate(x, weight, weight_per_head, gate, normalise, eps, out, gate_p
     if weight is not None:
         y = y * (weight.float().view(heads, w) if weight_per_head else weight.float().view(1, w))
     if gate is not None:
-        y = y * torch.sigmoid(gate.float().reshape(t, heads, 1 if gate_per_head else w))
+        z = gate.float().reshape(t, heads, 1 if gate_per_head else w)
+        y = y * (z * torch.sigmoid(z) if gate_silu else torch.sigmoid(z))
     out.copy_(y.reshape(out.shape).to(out.dtype))
 
 
@@ -348,6 +353,7 @@ def mlstm_scan(qkv, q_off, k_off, v_off, gates, gate_bias, cap, q_scale, state, 
 def delta_scan(qkv, q_off, k_off, v_off, a, dt_bias, a_log, beta_pre, q_scale, state, ctx, heads, kv_heads, d, dv, out) -> None:
     cu, slots = ctx.cu_query_lens.tolist(), ctx.state_slots.tolist()
     rep = heads // kv_heads
+    per_head = a.shape[1] == heads and d != 1
     for b in range(ctx.num_seqs):
         st = state[slots[b]].view(heads, d, dv)
         for h in range(heads):
@@ -360,7 +366,8 @@ def delta_scan(qkv, q_off, k_off, v_off, a, dt_bias, a_log, beta_pre, q_scale, s
                 v = qkv[t, v_off + h * dv: v_off + (h + 1) * dv]
                 q = q / torch.sqrt(q.pow(2).sum() + 1e-6) * q_scale
                 k = k / torch.sqrt(k.pow(2).sum() + 1e-6)
-                decay = torch.exp(-rate * torch.nn.functional.softplus(a[t, h * d: (h + 1) * d] + dt_bias[h * d: (h + 1) * d]))
+                cols = slice(h, h + 1) if per_head else slice(h * d, (h + 1) * d)
+                decay = torch.exp(-rate * torch.nn.functional.softplus(a[t, cols] + dt_bias[cols]))
                 S = decay[:, None] * S
                 u = torch.sigmoid(beta_pre[t, h]) * (v - S.t() @ k)
                 S = S + torch.outer(k, u)
@@ -381,21 +388,110 @@ def causal_conv_silu(x, taps, state, ctx, out) -> None:
 
 
 def qkv_prepare(q_in, k_in, v_in, q_weight, k_weight, eps, cos, sin, rotary_dim, slots, k_cache, v_cache, page_size,
-                heads, kv_heads, d, dv, q_out) -> None:
+                heads, kv_heads, d, dv, q_out, q_bias=None, k_bias=None, v_bias=None) -> None:
     t = q_out.shape[0]
 
-    def prep(x, w, n):
+    def prep(x, w, n, bias=None):
         y = x.float().reshape(t, n, d)
+        if bias is not None:
+            y = y + bias.float().view(n, d)
         if w is not None:
             y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * w.float()
         return _rotate(y, cos, sin, rotary_dim, False)
 
-    q_out.copy_(prep(q_in, q_weight, heads).to(q_out.dtype))
+    q_out.copy_(prep(q_in, q_weight, heads, q_bias).to(q_out.dtype))
     if k_in is None:
         return
     page, off = slots.long() // page_size, slots.long() % page_size
-    k_cache[page, :, off] = prep(k_in, k_weight, kv_heads).to(k_cache.dtype)
-    v_cache[page, :, off] = v_in.reshape(t, kv_heads, dv)
+    k_cache[page, :, off] = prep(k_in, k_weight, kv_heads, k_bias).to(k_cache.dtype)
+    v = v_in.reshape(t, kv_heads, dv)
+    if v_bias is not None:
+        v = (v.float() + v_bias.float().view(kv_heads, dv)).to(v_cache.dtype)
+    v_cache[page, :, off] = v
+
+
+# ------------------------------------------------- linear attention without a correction term
+def _silu(z):
+    return z * torch.sigmoid(z)
+
+
+def linear_scan_bonus(r, k, v, w_pre, w_bias, bonus, state, ctx, heads, d, dv, out) -> None:
+    cu, slots = ctx.cu_query_lens.tolist(), ctx.state_slots.tolist()
+    for b in range(ctx.num_seqs):
+        st = state[slots[b]].view(heads, d, dv)
+        for h in range(heads):
+            S = st[h].clone()
+            u = bonus[h * d: (h + 1) * d].to(state.dtype)
+            for t in range(cu[b], cu[b + 1]):
+                rr, kk = r[t, h * d: (h + 1) * d].to(state.dtype), k[t, h * d: (h + 1) * d].to(state.dtype)
+                vv = v[t, h * dv: (h + 1) * dv].to(state.dtype)
+                kv = torch.outer(kk, vv)
+                out[t, h] = (S + u[:, None] * kv).t() @ rr
+                w = torch.exp(-torch.exp(w_pre[t, h * d: (h + 1) * d] + w_bias[h * d: (h + 1) * d]))
+                S = w[:, None] * S + kv
+            st[h] = S
+
+
+def linear_scan_decay(q, k, v, decay, state, ctx, heads, d, dv, out) -> None:
+    cu, slots = ctx.cu_query_lens.tolist(), ctx.state_slots.tolist()
+    for b in range(ctx.num_seqs):
+        st = state[slots[b]].view(heads, d, dv)
+        for h in range(heads):
+            S = st[h].clone()
+            for t in range(cu[b], cu[b + 1]):
+                qq, kk = _silu(q[t, h * d: (h + 1) * d].to(state.dtype)), _silu(k[t, h * d: (h + 1) * d].to(state.dtype))
+                vv = _silu(v[t, h * dv: (h + 1) * dv].to(state.dtype))
+                S = decay[h] * S + torch.outer(kk, vv)
+                out[t, h] = S.t() @ qq
+            st[h] = S
+
+
+def token_shift_mix(x, mu, state, ctx, out) -> None:
+    cu, slots = ctx.cu_query_lens.tolist(), ctx.state_slots.tolist()
+    for b in range(ctx.num_seqs):
+        lo, hi = cu[b], cu[b + 1]
+        if hi <= lo:
+            continue
+        cur = x[lo:hi].to(state.dtype)
+        before = torch.cat([state[slots[b]].view(1, -1), cur[:-1]])
+        out[:, lo:hi] = (cur[None] + (before - cur)[None] * mu.to(state.dtype)[:, None, :]).to(out.dtype)
+        state[slots[b]] = cur[-1]
+
+
+# ------------------------------------------------------- around the residual stream
+def embed_pos_norm(tokens, positions, table, pos_table, norm_weight, eps, out, scale=1.0) -> None:
+    x = table[tokens.long()].float() * scale
+    if pos_table is not None:
+        x = x + pos_table[positions.long()].float()
+    if norm_weight is not None:
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * norm_weight.float()
+    out.copy_(x)
+
+
+def stream_sum(resid, terms, scales, bias=None, bias_scale=1.0, copy=None) -> None:
+    x = resid.clone()
+    for y, s in zip(terms, scales):
+        x = x + float(s) * y.float()
+    if bias is not None:
+        x = x + float(bias_scale) * bias.float()
+    resid.copy_(x)
+    if copy is not None:
+        copy.copy_(x.to(copy.dtype))
+
+
+def add_bias(y, bias) -> None:
+    y.copy_((y.float() + bias.float()).to(y.dtype))
+
+
+def tanh_(x) -> None:
+    x.copy_(torch.tanh(x.float()).to(x.dtype))
+
+
+def act_mul_gather(x, rows, table, col0, out, activation) -> None:
+    n = out.shape[1]
+    z = x.float()
+    a = _silu(z) if activation == "silu" else 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
+    out.copy_((a * table[rows.long(), col0: col0 + n].float()).to(out.dtype))
 
 
 # ---------------------------------------------------------------------- sampling
@@ -467,7 +563,8 @@ _NAMES = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_writ
           "gemm", "gemm_simt", "gemm_swiglu", "sample", "hc_mix_norm", "hc_collapse", "act_mul", "softcap",
           "head_norm_gate", "mlstm_scan", "delta_scan", "causal_conv_silu", "qkv_prepare", "gemm_gated",
           "post_norm_add_rms_norm", "latent_prepare", "latent_attention", "bmm", "transpose01", "moe_max_tiles", "moe_tile_rows", "moe_route_from",
-          "moe_route", "moe_gemm", "moe_combine"]
+          "moe_route", "moe_gemm", "moe_combine", "linear_scan_bonus", "linear_scan_decay", "token_shift_mix",
+          "embed_pos_norm", "stream_sum", "add_bias", "tanh_", "act_mul_gather"]
 
 
 @contextmanager

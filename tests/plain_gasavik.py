@@ -127,7 +127,7 @@ def lightning_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], p: str, 
 def side_by_side(h: torch.Tensor, w: Mapping[str, torch.Tensor], p: str, m: Mapping[str, Any], eps: float) -> torch.Tensor:
     left = windowed_attention(h, w, p + "left.", m["left"], eps)
     right = lightning_attention(h, w, p + "right.", m["right"], eps)
-    return float(m["left_scale"]) * left + float(m["right_scale"]) * right
+    return float(m.get("left_scale", 1.0)) * left + float(m.get("right_scale", 1.0)) * right
 
 
 def wkv(h: torch.Tensor, w: Mapping[str, torch.Tensor], p: str, m: Mapping[str, Any], eps: float) -> torch.Tensor:
@@ -219,3 +219,11 @@ def forward(config: Mapping[str, Any], w: Mapping[str, torch.Tensor], tokens: li
         if after_layers is not None:
             after_layers.append(x.clone())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def greedy(config: Mapping[str, Any], w: Mapping[str, torch.Tensor], prompt: list[int], new_tokens: int) -> list[int]:
+    """The ``new_tokens`` most likely next tokens, one after the other (the whole sequence is run again each time)."""
+    seq = list(prompt)
+    for _ in range(new_tokens):
+        seq.append(int(forward(config, w, seq)[-1].argmax()))
+    return seq[len(prompt):]
