@@ -38,9 +38,15 @@ def _tol(dtype):
     return {"atol": 2e-5, "rtol": 2e-5} if dtype == torch.float32 else {"atol": 2e-2, "rtol": 2e-2}
 
 
+class Arena:
+    def take(self, shape, dtype):
+        return torch.empty(shape, dtype=dtype, device="cuda")
+
+
 class Ctx(FakeCtx):
     def __init__(self, query_lens, context_lens):
         super().__init__(query_lens, context_lens, device="cuda")
+        self.arena = Arena()
 
 
 # ------------------------------------------------------------ kernels one by one
@@ -248,7 +254,8 @@ def _kept_case(dtype, heads, groups, d, dv, page, lens, news, window, keep, far=
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads, groups, d, dv, page, window, keep", [
     (4, 2, 32, 16, 4, 7, 3), (8, 1, 48, 48, 16, 96, 20), (4, 2, 64, 64, 16, 40, 17), (2, 2, 24, 40, 8, 19, 30), (6, 3, 96, 48, 16, 33, 1),
-    (4, 4, 64, 64, 16, 1, 1), (3, 1, 16, 16, 8, 5, 64)])
+    (4, 4, 64, 64, 16, 1, 1), (3, 1, 16, 16, 8, 5, 64), (4, 1, 128, 128, 16, 100, 130), (8, 2, 128, 128, 32, 200, 5),
+    (6, 3, 64, 64, 8, 60, 129), (2, 1, 128, 128, 16, 128, 128)])
 def test_attention_that_keeps_the_first_tokens_kernels(dtype, heads, groups, d, dv, page, window, keep) -> None:
     lens, news = [page * 3 + 1, 170, page * 2, 33, 1, 400], [1, 17, 1, 33, 1, 130]
     got, want, *_ = _kept_case(dtype, heads, groups, d, dv, page, lens, news, window, keep)
@@ -258,11 +265,12 @@ def test_attention_that_keeps_the_first_tokens_kernels(dtype, heads, groups, d, 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("new", [1, 2, 70])
-@pytest.mark.parametrize("window, keep, page", [(16, 5, 16), (33, 16, 16), (40, 17, 8), (7, 40, 4)])
-def test_edges_of_the_window_and_of_the_kept_tokens(dtype, new, window, keep, page) -> None:
+@pytest.mark.parametrize("window, keep, page, d", [(16, 5, 16, 32), (33, 16, 16, 64), (40, 17, 8, 128), (7, 40, 4, 32), (100, 140, 16, 64)])
+def test_edges_of_the_window_and_of_the_kept_tokens(dtype, new, window, keep, page, d) -> None:
     """The last query of a long request points at one key: it takes that key's value exactly when the key is
-    inside the window or among the kept first tokens; keys in prompts and among the step's own tokens."""
-    heads, groups, d, total = 4, 2, 32, 300
+    inside the window or among the kept first tokens; keys in prompts and among the step's own tokens. Head
+    sizes of 64 and 128 in bfloat16 run the prompt's rows on the tensor cores."""
+    heads, groups, total = 4, 2, 300
     last = total - 1
     for far in (0, keep - 1, keep, keep + 1, last - window, last - window + 1, last - 1, last):
         if not 0 <= far <= last:
@@ -298,8 +306,8 @@ def oracle(folders):
 
 def _check(got, reqs, want, dtype, what) -> None:
     assert all(sorted(got[rid]) == list(range(len(reqs[rid]))) for rid in got)
-    for rid in got:
-        assert_rows_close(torch.stack([got[rid][p] for p in range(len(reqs[rid]))]), *want[rid], dtype, f"{what}, {rid}")
+    rows = torch.cat([torch.stack([got[rid][p] for p in range(len(reqs[rid]))]) for rid in got])
+    assert_rows_close(rows, torch.cat([want[rid][0] for rid in got]), torch.cat([want[rid][1] for rid in got]), dtype, what)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

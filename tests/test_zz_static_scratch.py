@@ -96,7 +96,7 @@ def test_static_scratch_entry_point_matches_the_regular_one(dtype, hq, hkv, d, s
             q.data_ptr(), want.data_ptr(), k.data_ptr(), v.data_ptr(), tables.data_ptr(), tables.shape[1],
             cu.data_ptr(), ctx.data_ptr(), seqs.data_ptr(), b, seqs.data_ptr(), 0, 1, hq, hkv, d, page,
             d ** -0.5, window, splits, acc.data_ptr() if splits > 1 else None, ml.data_ptr() if splits > 1 else None,
-            None, 0, code, stream)
+            None, 0, 0, code, stream)
         assert st == 0
         torch.cuda.synchronize()
         assert not got.isnan().any()

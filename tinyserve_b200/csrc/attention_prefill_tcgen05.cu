@@ -140,7 +140,12 @@ __global__ void __launch_bounds__((4 * (NQ == 1 ? 2 : 1) * NQ + 2 * (NQ == 1 ? 2
   const int p_hi = p_lo + valid - 1;                          // position of the last live row
   const int lo = a.window > 0 ? max(0, p_lo - a.window + 1) : 0;   // first key any row sees
   const int t_begin = lo / BN;
-  const int n_tiles = (p_hi + 1 + BN - 1) / BN - t_begin;     // >= 1
+  // With kept first keys (positions below keep_first stay visible whatever the window) the tiles that
+  // hold any of them and lie in front of the window's first tile come first; the others follow.
+  const int kept = a.window > 0 ? min(a.keep_first, lo) : 0;  // kept keys below the window
+  const int kept_tiles = min(t_begin, (kept + BN - 1) / BN);
+  const int n_tiles = (p_hi + 1 + BN - 1) / BN - t_begin + kept_tiles;     // >= 1
+  auto tile_of = [&](int j) -> int { return j < kept_tiles ? j : t_begin + j - kept_tiles; };
   const int head0 = (int)blockIdx.x * NQ;
   const int kvh = head0 / (a.num_heads / a.num_kv_heads);
 
@@ -235,7 +240,7 @@ __global__ void __launch_bounds__((4 * (NQ == 1 ? 2 : 1) * NQ + 2 * (NQ == 1 ? 2
       tc_fence_after();
       uint32_t sraw[HC];
       float mx = -INFINITY;
-      const int k0 = (t_begin + j) * BN + half * HC;           // the first key of this thread's columns
+      const int k0 = tile_of(j) * BN + half * HC;              // the first key of this thread's columns
       if (ok) {
 #pragma unroll
         for (int c = 0; c < HC / 32; ++c) tmem_ld_32_nowait(tmem_sp + half * HC + c * 32, sraw + c * 32);
@@ -247,7 +252,7 @@ __global__ void __launch_bounds__((4 * (NQ == 1 ? 2 : 1) * NQ + 2 * (NQ == 1 ? 2
 #pragma unroll
           for (int i = 0; i < HC; ++i) {
             const int kpos = k0 + i;
-            const float v = (kpos <= p_abs && kpos >= first) ? __uint_as_float(sraw[i]) : -INFINITY;
+            const float v = (kpos <= p_abs && (kpos >= first || kpos < a.keep_first)) ? __uint_as_float(sraw[i]) : -INFINITY;
             sraw[i] = __float_as_uint(v);
             mx4[i & 3] = fmaxf(mx4[i & 3], v);
           }
@@ -352,6 +357,7 @@ __global__ void __launch_bounds__((4 * (NQ == 1 ? 2 : 1) * NQ + 2 * (NQ == 1 ? 2
     constexpr int COPIES = PARTS * D64;                         // per tile and tensor: one lane each
     static_assert(COPIES <= 32, "a lane issues at most one copy per tile and tensor");
     const int kmin = lo & ~(BR - 1), kmax = (ctx - 1) & ~(BR - 1);
+    const int kept_end = (kept + BR - 1) & ~(BR - 1);           // parts below this hold a kept key
     const int copy = lane * PW + pw;                            // this lane's copy of a tile
     const int part = copy / D64, h = copy - part * D64;         // its part of the tile and half of the head
     // The row of the cache tensors where this lane's part of tile j begins: a look-up in the block
@@ -361,7 +367,10 @@ __global__ void __launch_bounds__((4 * (NQ == 1 ? 2 : 1) * NQ + 2 * (NQ == 1 ? 2
     auto cache_row = [&](int j) -> int {
       // a part wholly outside the live keys is fetched from the nearest live part (its scores are
       // masked and its value rows zeroed); every part lies within one page
-      const int kpos = min(max((t_begin + j) * BN + part * BR, kmin), kmax);
+      // (live: in the window of some row, or among the kept first keys, whose pages are never given back)
+      int kpos = tile_of(j) * BN + part * BR;
+      if (kpos >= kept_end && kpos < kmin) kpos = kmin;
+      kpos = min(kpos, kmax);
       int page, off;
       if (a.page_shift >= 0) { page = table[kpos >> a.page_shift]; off = kpos & (a.page_size - 1); }
       else { const int idx = kpos / a.page_size; page = table[idx]; off = kpos - idx * a.page_size; }
@@ -444,13 +453,13 @@ __global__ void __launch_bounds__((4 * (NQ == 1 ? 2 : 1) * NQ + 2 * (NQ == 1 ? 2
     auto v_ready = [&](int j) -> bool {
       const int st = j % FA_KV_STAGES;
       if (!fa_warp_wait(&v_full[st], (j / FA_KV_STAGES) & 1, failed)) return false;
-      const int k0 = (t_begin + j) * BN;
+      const int k0 = tile_of(j) * BN;
       if (k0 < lo || k0 + BN > ctx) {
         unsigned char* v_tile = smem + L::OFF_V + st * L::KV_BYTES;
         for (int idx = lane; idx < BN * D64 * 8; idx += 32) {
           const int row = idx / (D64 * 8), c = idx - row * (D64 * 8);
           const int kpos = k0 + row;
-          if (kpos < lo || kpos >= ctx)
+          if ((kpos < lo && kpos >= kept) || kpos >= ctx)
             *reinterpret_cast<uint4*>(v_tile + (c >> 3) * (BN * 128) + row * 128 + ((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
         }
         fence_proxy_async_smem();
@@ -552,12 +561,13 @@ extern "C" int ts_prefill_attention_tcgen05(
     const void* q, void* out, const void* k_cache, const void* v_cache, long long num_pages_total,
     const int* block_tables, int table_width, const int* cu_q, const int* ctx_lens, const int* prefill_seqs,
     int num_prefill, int max_query_len, int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
-    int window, int heads_per_cta, int* error_flag, const float* sinks, cudaStream_t stream) {
+    int window, int heads_per_cta, int* error_flag, const float* sinks, int keep_first, cudaStream_t stream) {
+  // `keep_first` (with a window): positions below it stay visible to every later query
   // `sinks` (optional, [num_heads] float): a logit per head that joins the softmax's denominator without a value
   if (num_prefill <= 0 || max_query_len <= 0) return 0;
   if ((head_dim != 64 && head_dim != 128) || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
   if (!(page_size == 8 || (page_size > 0 && page_size % 16 == 0))) return TS_ERR_UNSUPPORTED;
-  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || window < 0 || num_pages_total <= 0) return TS_ERR_BAD_ARGUMENT;
+  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || window < 0 || keep_first < 0 || num_pages_total <= 0) return TS_ERR_BAD_ARGUMENT;
   if ((((uintptr_t)k_cache) | ((uintptr_t)v_cache) | ((uintptr_t)q) | ((uintptr_t)out)) & 15) return TS_ERR_UNSUPPORTED;
   const long long rows = num_pages_total * num_kv_heads * page_size;
   if (rows >= (1ll << 31)) return TS_ERR_UNSUPPORTED;
@@ -574,6 +584,7 @@ extern "C" int ts_prefill_attention_tcgen05(
   a.page_shift = page_shift_of(page_size);
   a.scale_log2 = scale * 1.4426950408889634f;
   a.window = window;
+  a.keep_first = window > 0 ? keep_first : 0;
   a.num_splits = 1; a.part_acc = nullptr; a.part_ml = nullptr;
 #define TS_FA(D64_, BR_)                                                                                \
   return heads_per_cta == 2 ? launch_fa<D64_, BR_, 2>(a, rows, max_query_len, error_flag, stream)       \

@@ -65,7 +65,7 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_prefill_attention_tma": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f,
                                  _i, _vp, _vp],
     "ts_prefill_attention_tcgen05": [_vp, _vp, _vp, _vp, _c.c_longlong, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                     _f, _i, _i, _vp, _vp, _vp],
+                                     _f, _i, _i, _vp, _vp, _i, _vp],
     "ts_gemm_skinny_normed": [_vp, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "ts_gemm_skinny_to_stream": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "ts_gemm_skinny_to_stream_parts": [_i, _i, _i],
@@ -440,8 +440,9 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     keep_first = int(keep_first) if window > 0 else 0
     if keep_first < 0:
         raise KernelError("paged_attention: keep_first must not be negative")
-    simt_only = (dv != d or d % 16 != 0 or keep_first > 0
-                 or (sinks is not None and not (tma_ok and PREFILL_ATTENTION == "tcgen05")))
+    # kept first positions are known to the tcgen05 prompt kernel and the CUDA-core kernels
+    simt_only = (dv != d or d % 16 != 0
+                 or ((sinks is not None or keep_first > 0) and not (tma_ok and PREFILL_ATTENTION == "tcgen05")))
     if d > 256 or dv > 256:
         raise KernelError(f"paged_attention: head sizes {d}/{dv} must be at most 256")
     if block_tables.dim() != 2 or block_tables.shape[0] != ctx.num_seqs:
@@ -467,7 +468,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                 _dev(ctx.prefill_seqs, "prefill_seqs", torch.int32), num_prefill, ctx.max_query_len,
                 hq, hkv, d, page_size, float(scale), int(window),
                 _prefill_heads_per_cta(ctx, hq, hkv),
-                _error_word(q.device).data_ptr(), _opt(sinks, "sinks", torch.float32), _stream()),
+                _error_word(q.device).data_ptr(), _opt(sinks, "sinks", torch.float32), keep_first, _stream()),
                 "prefill_attention_tcgen05")
         elif tma_ok:
             _check(_fn("ts_prefill_attention_tma")(
@@ -489,6 +490,11 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         num_prefill = 0
         if not ctx.num_decode:
             return
+    if keep_first > 0:
+        # single tokens over a window and the kept first positions: the CUDA-core kernel, which walks the two
+        # runs of keys as one and splits them over CTAs
+        _paged_attention_simt(q, k_cache, v_cache, page_size, block_tables, ctx, scale, window, out, sinks, num_prefill, keep_first)
+        return
     if dt == torch.bfloat16 and d <= 128:
         # decode rows on the tensor cores too: one CTA per (request, kv group, key range)
         ctas = ctx.num_decode * hkv * (-(-(hq // hkv) // 16))
