@@ -1,4 +1,4 @@
-"""``python bench.py --designs [--design fegilix|guzovik]``: prefill and decode throughput of a
+"""``python bench.py --designs [--design fegilix|guzovik|gasavik]``: prefill and decode throughput of a
 design at layer sizes that resemble a real model's (random weights), beside the dense Qwen3 decoder,
 the closest existing model, with the same width, attention heads, (active) feed-forward size and
 number of layers; and where each design's step time goes, kernel class by kernel class, with the
@@ -67,10 +67,29 @@ def guzovik_config(s: dict) -> dict:
                        {"type": "latent_attention", "mlp": moe, "mixer": latent}, dict(shared_layer)]}
 
 
-DESIGNS = {"fegilix": fegilix_config, "guzovik": guzovik_config}
+def gasavik_config(s: dict) -> dict:
+    """Windowed attention that keeps the first tokens beside decayed linear attention, time mixing twice, the
+    gated delta rule, the pair again, time mixing; every layer with the dense model's feed-forward beside its
+    mixer and a token input of 256 columns behind it. Time mixing with heads of 64 that fill the width."""
+    pair = {"left": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+                     "mask": {"size": 512, "keep_first": 16}},
+            "right": {"heads": s["rec_heads"], "dim": s["dim"], "vdim": s["dim"],
+                      "decay": [1.0 - 2.0 ** -(2 + 6 * i / max(1, s["rec_heads"] - 1)) for i in range(s["rec_heads"])]},
+            "left_scale": 0.6, "right_scale": 0.5}
+    mlp = {"kind": "dense", "ff": s["ff"]}
+    wkv = {"type": "wkv", "mlp": mlp, "mixer": {"heads": s["width"] // 64, "dim": 64, "decay_rank": 64}}
+    delta = {"type": "delta", "mlp": mlp, "mixer": {"heads": s["rec_heads"], "kv_heads": max(1, s["rec_heads"] // 2), "dim": s["dim"],
+                                                     "vdim": s["dim"], "conv": 4}}
+    par = {"type": "parallel", "mlp": mlp, "mixer": pair}
+    return {"architecture": "Gasavik", "vocab": VOCAB, "width": s["width"], "max_positions": 8192, "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "token_side": {"dim": 256}, "layers": [par, wkv, wkv, delta, par, wkv]}
+
+
+DESIGNS = {"fegilix": fegilix_config, "guzovik": guzovik_config, "gasavik": gasavik_config}
 NEW_OPS = ["post_norm_add_rms_norm", "latent_prepare", "latent_attention", "bmm", "transpose01", "moe_route_from", "moe_route", "moe_gemm",
            "moe_combine", "gemm_gated", "hc_mix_norm", "hc_collapse", "act_mul", "softcap", "head_norm_gate", "mlstm_scan", "delta_scan",
-           "causal_conv_silu", "qkv_prepare"]
+           "causal_conv_silu", "qkv_prepare", "linear_scan_bonus", "linear_scan_decay", "token_shift_mix", "embed_pos_norm",
+           "stream_sum", "add_bias", "tanh_", "act_mul_gather"]
 OLD_OPS = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_write", "paged_attention",
            "decode_attention_fused", "gemm", "gemm_swiglu", "gemm_to_stream", "gemm_normed", "sample"]
 
@@ -196,6 +215,22 @@ class DesignBench(Bench):
                 return (2.0 * ctx.num_seqs * heads * d * dv * 4 + nbytes(a[0], a[4], a[7], a[15]), 8.0 * a[0].shape[0] * heads * d * dv)
             if name == "causal_conv_silu":
                 return nbytes(a[0], a[4]), 0.0
+            if name == "linear_scan_bonus":   # state in and out, r, k, v and the decays read, the read-out written; 6 flops per state element and token
+                ctx, heads, d, dv = a[7], a[8], a[9], a[10]
+                return (2.0 * ctx.num_seqs * heads * d * dv * 4 + nbytes(a[0], a[1], a[2], a[3], a[11]), 6.0 * a[0].shape[0] * heads * d * dv)
+            if name == "linear_scan_decay":   # 4 flops per state element and token
+                ctx, heads, d, dv = a[5], a[6], a[7], a[8]
+                return (2.0 * ctx.num_seqs * heads * d * dv * 4 + nbytes(a[0], a[1], a[2], a[9]), 4.0 * a[0].shape[0] * heads * d * dv)
+            if name == "token_shift_mix":
+                return nbytes(a[0], a[4]), 0.0
+            if name == "stream_sum":          # the stream read and written, every term read, the copy written
+                return 2.0 * nbytes(a[0]) + nbytes(*a[1]) + nbytes(k.get("copy")), 0.0
+            if name == "embed_pos_norm":
+                return nbytes(a[6]) * (1.0 + 2.0 * a[2].element_size() / 4.0), 0.0
+            if name == "act_mul_gather":
+                return nbytes(a[0], a[4]) * 1.5, 0.0
+            if name in ("add_bias", "tanh_"):
+                return 2.0 * nbytes(a[0]), 0.0
             if name == "hc_mix_norm":         # the lanes read and written, the pending output, the result
                 return 2.0 * nbytes(a[0]) + nbytes(a[2], a[8]), 0.0
             if name == "hc_collapse":

@@ -196,6 +196,10 @@ def act_mul(gate_up, out, activation, limit=0.0, bias=None) -> None:
     out.copy_((a * u).to(out.dtype))
 
 
+def gemm_biased_swiglu(x, w_gate_up, bias, out, arena=None) -> None:
+    act_mul(x.float() @ w_gate_up.float().t(), out, "silu", bias=bias)
+
+
 def gemm_gated(x, w_gate_up, out, arena, activation, limit=0.0) -> None:
     if activation == "silu":
         gemm_swiglu(x, w_gate_up, out, arena)
@@ -564,7 +568,7 @@ _NAMES = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_writ
           "head_norm_gate", "mlstm_scan", "delta_scan", "causal_conv_silu", "qkv_prepare", "gemm_gated",
           "post_norm_add_rms_norm", "latent_prepare", "latent_attention", "bmm", "transpose01", "moe_max_tiles", "moe_tile_rows", "moe_route_from",
           "moe_route", "moe_gemm", "moe_combine", "linear_scan_bonus", "linear_scan_decay", "token_shift_mix",
-          "embed_pos_norm", "stream_sum", "add_bias", "tanh_", "act_mul_gather"]
+          "embed_pos_norm", "stream_sum", "add_bias", "tanh_", "act_mul_gather", "gemm_biased_swiglu"]
 
 
 @contextmanager

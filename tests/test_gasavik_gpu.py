@@ -116,6 +116,22 @@ def test_gate_kernels(dtype) -> None:
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows, inter, k", [(1, 64, 128), (3, 48, 96), (8, 512, 256), (16, 1024, 1024), (29, 96, 64), (40, 96, 64),
+                                            (300, 1024, 256), (700, 2048, 512), (2048, 3072, 1024), (5, 20, 36), (260, 200, 72)])
+def test_feed_forward_product_with_biases(dtype, rows, inter, k) -> None:
+    """The three routes (few rows, tensor-core tiles of 128 and of 256 rows, product + activation kernel)."""
+    from tinyserve_b200.kernels import ops
+
+    x, w = _rand(rows, k, seed=1, dtype=dtype), _rand(2 * inter, k, seed=2, scale=k ** -0.5, dtype=dtype)
+    bias = _rand(2 * inter, seed=3, dtype=dtype)
+    a, b = torch.empty(rows, inter, dtype=dtype, device="cuda"), torch.empty(rows, inter, dtype=dtype, device="cuda")
+    ops.gemm_biased_swiglu(x, w, bias, a, Arena())
+    refs.gemm_biased_swiglu(x, w, bias, b)
+    ops.check_device_errors()
+    torch.testing.assert_close(a.float(), b.float(), **({"atol": 1e-4, "rtol": 1e-4} if dtype == torch.float32 else {"atol": 3e-2, "rtol": 3e-2}))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads, d, dv", [(2, 16, 16), (3, 40, 24), (1, 48, 70), (2, 64, 32), (1, 128, 64), (2, 8, 8)])
 def test_linear_scan_kernels(dtype, heads, d, dv) -> None:
     """Both forms over requests of unequal lengths (chunk edges at 16 and 8 tokens), the state in a column range of

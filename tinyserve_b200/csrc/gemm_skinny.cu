@@ -44,7 +44,14 @@ namespace ts {
 // separate kernels, FUSE_GELU_TANH = gelu_tanh(gate) * up in 32-bit, rounded once.
 // FUSE_CLAMPED_SWISH = with g = min(gate, limit), u = clamp(up, -limit, limit): g sigmoid(1.702 g) (u + 1)
 // in 32-bit, rounded once; the limit travels in SkinnyNorm::act_limit.
-constexpr int FUSE_GELU_TANH = 2, FUSE_CLAMPED_SWISH = 3;
+// FUSE_BIASED_SILU = silu(gate + b_gate) * (up + b_up) in 32-bit, rounded once; the biases (2 N values, gate
+// then up) travel in SkinnyNorm::act_bias.
+constexpr int FUSE_GELU_TANH = 2, FUSE_CLAMPED_SWISH = 3, FUSE_BIASED_SILU = 4;
+__device__ __forceinline__ float biased_silu_f(float g, float u, const __nv_bfloat16* bias, int col, int n) {
+  g += __bfloat162float(bias[col]);
+  u += __bfloat162float(bias[n + col]);
+  return g / (1.f + expf(-g)) * u;
+}
 __device__ __forceinline__ float clamped_swish_f(float g, float u, float limit) {
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
@@ -102,6 +109,7 @@ struct SkinnyNorm {
   bf16* resid16_out;      // RESID: [M, N] its bf16 copy
   float* sumsq_out;       // RESID: [M][N / 16]
   float act_limit;        // FUSE_CLAMPED_SWISH: the limit
+  const bf16* act_bias;   // FUSE_BIASED_SILU: [2 N] biases of gate and up
 };
 
 __device__ __forceinline__ uint4 ld_cg(const void* p) {
@@ -339,6 +347,8 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
           out[(size_t)m * N + n0 + row] = from_float<TOut>(gelu_tanh_f(s) * u);     // 32-bit, rounded once
         } else if constexpr (FUSE == FUSE_CLAMPED_SWISH) {
           out[(size_t)m * N + n0 + row] = from_float<TOut>(clamped_swish_f(s, u, nrm.act_limit));
+        } else if constexpr (FUSE == FUSE_BIASED_SILU) {
+          out[(size_t)m * N + n0 + row] = from_float<TOut>(biased_silu_f(s, u, nrm.act_bias, n0 + row, N));
         } else {
           const float gv = round_to<bf16>(s), uv = round_to<bf16>(u);
           const float sv = round_to<bf16>(gv / (1.f + expf(-gv)));
@@ -379,6 +389,8 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
         out[(size_t)m * N + n0 + row] = from_float<TOut>(gelu_tanh_f(s) * u);
       } else if constexpr (FUSE == FUSE_CLAMPED_SWISH) {
         out[(size_t)m * N + n0 + row] = from_float<TOut>(clamped_swish_f(s, u, nrm.act_limit));
+      } else if constexpr (FUSE == FUSE_BIASED_SILU) {
+        out[(size_t)m * N + n0 + row] = from_float<TOut>(biased_silu_f(s, u, nrm.act_bias, n0 + row, N));
       } else if constexpr (FUSE) {
         const float gv = round_to<bf16>(s), uvv = round_to<bf16>(u);
         const float act = round_to<bf16>(gv / (1.f + expf(-gv)));
@@ -733,6 +745,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_h8_kernel(const bf16* 
         out[(size_t)om * N + n0 + orow] = from_float<TOut>(gelu_tanh_f(s) * u);     // 32-bit, rounded once
       } else if constexpr (FUSE == FUSE_CLAMPED_SWISH) {
         out[(size_t)om * N + n0 + orow] = from_float<TOut>(clamped_swish_f(s, u, nrm.act_limit));
+      } else if constexpr (FUSE == FUSE_BIASED_SILU) {
+        out[(size_t)om * N + n0 + orow] = from_float<TOut>(biased_silu_f(s, u, nrm.act_bias, n0 + orow, N));
       } else {
         const float gv = round_to<bf16>(s), uv = round_to<bf16>(u);
         const float sv = round_to<bf16>(gv / (1.f + expf(-gv)));
@@ -761,9 +775,10 @@ static bool normed_takes_h8(int M, int N, int K) { return M <= 16 && h8_spreads_
 // The plain and the SwiGLU product of up to 16 rows: narrow outputs take the tall CTAs, wide ones CTAs of 8 warps.
 template <typename TOut, int FUSE>
 static int launch_h8_plain(const bf16* x, const bf16* w, TOut* out, int M, int N, int K, cudaStream_t stream,
-                           float act_limit = 0.f) {
+                           float act_limit = 0.f, const bf16* act_bias = nullptr) {
   SkinnyNorm nrm = SkinnyNorm();
   nrm.act_limit = act_limit;
+  nrm.act_bias = act_bias;
   if (K <= SK_H8_PF * SK_H8_WARPS * 32) {
     if (M <= 8) return launch(gemm_skinny_h8_kernel<TOut, FUSE, false, false, SK_H8_WARPS, SK_H8_PF, 1>, N / 8, SK_H8_WARPS * 32, 0, stream, x, w, out, M, N, K, nrm);
     return launch(gemm_skinny_h8_kernel<TOut, FUSE, false, false, SK_H8_WARPS, SK_H8_PF, 2>, N / 8, SK_H8_WARPS * 32, 0, stream, x, w, out, M, N, K, nrm);
@@ -797,9 +812,10 @@ static int dispatch_skinny(const bf16* x, const bf16* w, TOut* out, int M, int N
 
 template <int NT, int FUSE = 1>
 static int dispatch_swiglu_nt(const bf16* x, const bf16* w, bf16* out, int M, int inter, int K, cudaStream_t stream,
-                              float act_limit = 0.f) {
+                              float act_limit = 0.f, const bf16* act_bias = nullptr) {
   SkinnyNorm nrm = SkinnyNorm();
   nrm.act_limit = act_limit;
+  nrm.act_bias = act_bias;
   return launch_skinny<bf16, NT, 1, FUSE, 4>(x, w, out, M, inter, K, stream, nrm);
 }
 
@@ -859,6 +875,23 @@ extern "C" int ts_gemm_skinny_gated(const void* x, const void* w, void* out, int
   if (M <= 8) return dispatch_swiglu_nt<1, FUSE_GELU_TANH>(xp, wp, op, M, inter, K, stream);
   if (M <= 16) return dispatch_swiglu_nt<2, FUSE_GELU_TANH>(xp, wp, op, M, inter, K, stream);
   return dispatch_swiglu_nt<4, FUSE_GELU_TANH>(xp, wp, op, M, inter, K, stream);
+}
+
+// silu(x gate^T + b_gate) * (x up^T + b_up) in 32-bit, rounded once; bias [2 inter] bf16 (gate, then up).
+extern "C" int ts_gemm_skinny_biased_swiglu(const void* x, const void* w, const void* bias, void* out, int M, int inter,
+                                            int K, cudaStream_t stream) {
+  if (M <= 0 || inter <= 0) return 0;
+  if (!bias) return TS_ERR_BAD_ARGUMENT;
+  if (M > 32 || K <= 0 || K % 32 != 0 || inter % 16 != 0) return TS_ERR_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return TS_ERR_UNSUPPORTED;
+  const bf16* xp = (const bf16*)x;
+  const bf16* wp = (const bf16*)w;
+  const bf16* bp = (const bf16*)bias;
+  bf16* op = (bf16*)out;
+  if (plain_takes_h8(M, inter, K)) return launch_h8_plain<bf16, FUSE_BIASED_SILU>(xp, wp, op, M, inter, K, stream, 0.f, bp);
+  if (M <= 8) return dispatch_swiglu_nt<1, FUSE_BIASED_SILU>(xp, wp, op, M, inter, K, stream, 0.f, bp);
+  if (M <= 16) return dispatch_swiglu_nt<2, FUSE_BIASED_SILU>(xp, wp, op, M, inter, K, stream, 0.f, bp);
+  return dispatch_swiglu_nt<4, FUSE_BIASED_SILU>(xp, wp, op, M, inter, K, stream, 0.f, bp);
 }
 
 // out = rms_norm(resid) * w^T where the norm is made on the fly (NORMX above): resid16 [M, K] bf16,

@@ -39,11 +39,13 @@ constexpr int TG_THREADS = 192;     // TMA warp, MMA warp, four epilogue warps
 // of the separate kernels, GATED_GELU_TANH = gelu_tanh(gate) * up in 32-bit.
 // GATED_CLAMPED_SWISH = with g = min(gate, limit) and u = clamp(up, -limit, limit): g sigmoid(1.702 g) (u + 1)
 // in 32-bit, rounded once (`act_limit` is the limit; the other forms ignore it).
-constexpr int GATED_SILU = 1, GATED_GELU_TANH = 2, GATED_CLAMPED_SWISH = 3;
+// GATED_BIASED_SILU = silu(gate + b_gate) * (up + b_up) in 32-bit, rounded once; `act_bias` holds the 2 N biases,
+// gate then up.
+constexpr int GATED_SILU = 1, GATED_GELU_TANH = 2, GATED_CLAMPED_SWISH = 3, GATED_BIASED_SILU = 4;
 
 template <int BN, typename TOut, int SWIGLU>
 __device__ __forceinline__ void drain_tile(uint32_t tmem_acc, int row, int M, int N, int n0, TOut* __restrict__ out,
-                                           float act_limit) {
+                                           float act_limit, const bf16* __restrict__ act_bias) {
   constexpr int BN_OUT = SWIGLU ? BN / 2 : BN;
   if constexpr (SWIGLU) {
 #pragma unroll 1
@@ -65,6 +67,10 @@ __device__ __forceinline__ void drain_tile(uint32_t tmem_acc, int row, int M, in
             float th;
             asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * fmaf(0.044715f * z * z, z, z)));
             f[j] = 0.5f * z * (1.f + th) * __uint_as_float(u[j]);
+          } else if constexpr (SWIGLU == GATED_BIASED_SILU) {
+            const int col = min(n0 + c * 32 + j, N - 1);          // columns past the edge are computed and not stored
+            const float gv = __uint_as_float(g[j]) + to_float(act_bias[col]);
+            f[j] = __fdividef(gv, 1.f + __expf(-gv)) * (__uint_as_float(u[j]) + to_float(act_bias[N + col]));
           } else if constexpr (SWIGLU == GATED_CLAMPED_SWISH) {
             const float gv = fminf(__uint_as_float(g[j]), act_limit);
             const float uv = fminf(fmaxf(__uint_as_float(u[j]), -act_limit), act_limit);
@@ -141,7 +147,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
                                                                   const __grid_constant__ CUtensorMap map_w,
                                                                   TOut* __restrict__ out, int M, int N, int K,
                                                                   int* __restrict__ error_flag, float act_limit,
-                                                                  GemmGroup grp) {
+                                                                  GemmGroup grp, const bf16* __restrict__ act_bias) {
   constexpr uint32_t A_BYTES = TG_BM * TG_BK * 2, B_BYTES = BN * TG_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   // instruction descriptor: D = f32, A = B = bf16, both K-major, N = BN, M = 128
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TG_BM >> 4) << 24);
@@ -263,7 +269,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
       }
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
-      drain_tile<BN, TOut, SWIGLU>(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * BN), row, m_end, N, n0, out, act_limit);
+      drain_tile<BN, TOut, SWIGLU>(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * BN), row, m_end, N, n0, out, act_limit, act_bias);
       // this warp has read its part of the accumulator: hand the buffer back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -288,7 +294,8 @@ template <int STAGES, typename TOut, int SWIGLU>
 __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                        const __grid_constant__ CUtensorMap map_w,
                                                                        TOut* __restrict__ out, int M, int N, int K,
-                                                                       int* __restrict__ error_flag, float act_limit) {
+                                                                       int* __restrict__ error_flag, float act_limit,
+                                                                       const bf16* __restrict__ act_bias) {
   constexpr int BN = 256, PAIR_BM = 2 * TG_BM;
   constexpr uint32_t A_BYTES = TG_BM * TG_BK * 2, B_BYTES = (BN / 2) * TG_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // per CTA
   // instruction descriptor: D = f32, A = B = bf16, both K-major, N = 256, M = 256 over the pair
@@ -400,7 +407,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_pair_kernel(const __g
       }
       tc_fence_after();
       drain_tile<BN, TOut, SWIGLU>(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * BN), m0 + quad * 32 + lane, M, N,
-                                   n0, out, act_limit);
+                                   n0, out, act_limit, act_bias);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8u * b);
@@ -445,7 +452,8 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int bo
 
 template <int BN, int STAGES, typename TOut, int SWIGLU = false>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, TOut* out, int M, int N, int K, int* error_flag,
-                     cudaStream_t stream, float act_limit = 0.f, const GemmGroup& grp = GemmGroup(), int max_row_tiles = 0) {
+                     cudaStream_t stream, float act_limit = 0.f, const GemmGroup& grp = GemmGroup(), int max_row_tiles = 0,
+                     const bf16* act_bias = nullptr) {
   const size_t smem = (size_t)STAGES * (TG_BM + BN) * TG_BK * 2 + 1024;
   auto kern = gemm_tcgen05_kernel<BN, STAGES, TOut, SWIGLU>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -454,12 +462,12 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, TOut* out, in
   const int row_tiles = grp.tile_expert ? max_row_tiles : (M + TG_BM - 1) / TG_BM;
   const int num_tiles = ((N + BN_OUT - 1) / BN_OUT) * row_tiles;
   const int ctas = num_tiles < 148 ? num_tiles : 148;     // one persistent CTA per SM
-  return launch(kern, ctas, TG_THREADS, smem, stream, mx, mw, out, M, N, K, error_flag, act_limit, grp);
+  return launch(kern, ctas, TG_THREADS, smem, stream, mx, mw, out, M, N, K, error_flag, act_limit, grp, act_bias);
 }
 
 template <int STAGES, typename TOut, int SWIGLU>
 static int launch_tc_pair(const CUtensorMap& mx, const CUtensorMap& mw, TOut* out, int M, int N, int K, int* error_flag,
-                          cudaStream_t stream, float act_limit = 0.f) {
+                          cudaStream_t stream, float act_limit = 0.f, const bf16* act_bias = nullptr) {
   const size_t smem = (size_t)STAGES * (TG_BM + 128) * TG_BK * 2 + 1024;
   auto kern = gemm_tcgen05_pair_kernel<STAGES, TOut, SWIGLU>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -467,7 +475,7 @@ static int launch_tc_pair(const CUtensorMap& mx, const CUtensorMap& mw, TOut* ou
   constexpr int BN_OUT = SWIGLU ? 128 : 256;
   const int num_tiles = ((N + BN_OUT - 1) / BN_OUT) * ((M + 2 * TG_BM - 1) / (2 * TG_BM));
   const int pairs = num_tiles < 74 ? num_tiles : 74;      // one persistent CTA per SM, two SMs a pair
-  return launch_cluster(kern, dim3(2 * pairs), dim3(TG_THREADS), smem, stream, dim3(2, 1, 1), mx, mw, out, M, N, K, error_flag, act_limit);
+  return launch_cluster(kern, dim3(2 * pairs), dim3(TG_THREADS), smem, stream, dim3(2, 1, 1), mx, mw, out, M, N, K, error_flag, act_limit, act_bias);
 }
 
 }  // namespace ts
@@ -511,6 +519,20 @@ extern "C" int ts_gemm_tcgen05_swiglu(const void* x, const void* w, void* out, i
   if (!make_map(&mx, x, M, K, TG_BM) || !make_map(&mw, w, 2 * inter, K, 128)) return TS_ERR_UNSUPPORTED;
   if (pair) return launch_tc_pair<6, bf16, GATED_SILU>(mx, mw, (bf16*)out, M, inter, K, error_flag, stream);
   return launch_tc<256, 4, bf16, GATED_SILU>(mx, mw, (bf16*)out, M, inter, K, error_flag, stream);
+}
+
+// silu(x gate^T + b_gate) * (x up^T + b_up) in 32-bit, rounded once; bias [2 inter] bf16 (gate, then up).
+extern "C" int ts_gemm_tcgen05_biased_swiglu(const void* x, const void* w, const void* bias, void* out, int M, int inter,
+                                             int K, int pair, int* error_flag, cudaStream_t stream) {
+  if (M <= 0 || inter <= 0) return 0;
+  if (!bias) return TS_ERR_BAD_ARGUMENT;
+  if (K <= 0 || K % 8 != 0 || error_flag == nullptr) return TS_ERR_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return TS_ERR_UNSUPPORTED;
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, M, K, TG_BM) || !make_map(&mw, w, 2 * inter, K, 128)) return TS_ERR_UNSUPPORTED;
+  if (pair) return launch_tc_pair<6, bf16, GATED_BIASED_SILU>(mx, mw, (bf16*)out, M, inter, K, error_flag, stream, 0.f, (const bf16*)bias);
+  return launch_tc<256, 4, bf16, GATED_BIASED_SILU>(mx, mw, (bf16*)out, M, inter, K, error_flag, stream, 0.f, GemmGroup(), 0,
+                                                    (const bf16*)bias);
 }
 
 // The same with a choice of activation: 0 = silu (as above), 1 = the tanh form of GELU, 2 = the clamped

@@ -77,6 +77,8 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_gemm_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ts_gemm_tcgen05_swiglu": [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "ts_gemm_tcgen05_gated": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp],
+    "ts_gemm_tcgen05_biased_swiglu": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
+    "ts_gemm_skinny_biased_swiglu": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "ts_gemm_skinny_gated": [_vp, _vp, _vp, _i, _i, _i, _i, _f, _vp],
     "ts_latent_prepare": [_vp, _c.c_longlong, _vp, _vp, _c.c_longlong, _vp, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i,
                           _i, _i, _i, _vp],
@@ -812,6 +814,33 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, are
     gate_up = arena.take((m, 2 * inter), x.dtype)
     gemm(x, w_gate_up, gate_up)
     silu_mul(gate_up, out)
+
+
+def gemm_biased_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, bias: torch.Tensor, out: torch.Tensor, arena: Any) -> None:
+    """``out[M, I] = silu(x Wgate^T + b_gate) * (x Wup^T + b_up)`` with ``bias [2 I]`` (gate, then up) in the model
+    dtype; the sums with the biases, the activation and the product of the halves are 32-bit, rounded once. The same
+    three routes as :func:`gemm_swiglu`: a few bf16 rows the skinny product, many bf16 rows of a wide matrix the tcgen05
+    product, each with the biases and the activation in its epilogue; anything else a product into scratch and the
+    activation kernel."""
+    m, k = x.shape
+    inter = out.shape[1]
+    if (tuple(w_gate_up.shape) != (2 * inter, k) or out.shape[0] != m or out.dtype != x.dtype or bias.shape != (2 * inter,)
+            or bias.dtype != x.dtype):
+        raise KernelError("gemm_biased_swiglu: shape or dtype mismatch")
+    if (x.dtype == torch.bfloat16 and m <= SKINNY_MAX_ROWS and k % 32 == 0 and inter % 16 == 0
+            and 2 * inter * k <= SKINNY_MAX_WEIGHTS):
+        _check(_fn("ts_gemm_skinny_biased_swiglu")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(bias, "bias"), _dev(out, "out"),
+                                                   m, inter, k, _stream()), "gemm_biased_swiglu")
+        return
+    tiles = tcgen05_tiles(m, inter, 128)
+    if x.dtype == torch.bfloat16 and m >= TCGEN05_MIN_ROWS and 2 * inter >= TCGEN05_MIN_COLS and k % 8 == 0 and tiles:
+        _check(_fn("ts_gemm_tcgen05_biased_swiglu")(_dev(x, "x"), _dev(w_gate_up, "w_gate_up"), _dev(bias, "bias"), _dev(out, "out"),
+                                                    m, inter, k, int(tiles == "pairs"), _error_word(x.device).data_ptr(),
+                                                    _stream()), "gemm_tcgen05_biased_swiglu")
+        return
+    gate_up = arena.take((m, 2 * inter), x.dtype)
+    gemm(x, w_gate_up, gate_up)
+    act_mul(gate_up, out, "silu", bias=bias)
 
 
 def gemm_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, arena: Any, activation: str,

@@ -61,8 +61,8 @@ class GatedMLP(FeedForward):
     (``names``: role "gate" / "up" / "down" -> name after the prefix). Gate and up come from one
     product with the merged matrix, with the activation in the same kernel where the framework
     has one for the step's shape (``ops.gemm_gated``). With ``bias`` every projection has a bias
-    (the projection's name with ``.b`` added): those of gate and up are added in the activation
-    kernel; the output's is ``output_bias``, which a block that sums the output into the stream
+    (the projection's name with ``.b`` added): those of gate and up are added where the activation is
+    applied (inside the product where the framework has such a kernel for the step's shape, ``ops.gemm_biased_swiglu``); the output's is ``output_bias``, which a block that sums the output into the stream
     itself may take over (``forward(..., add_output_bias=False)``)."""
 
     recordable = EVERY_STEP
@@ -105,7 +105,9 @@ class GatedMLP(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext, add_output_bias: bool = True) -> torch.Tensor:
         t = x.shape[0]
         act = ctx.arena.take((t, self.intermediate_size), ctx.dtype)
-        if self.bias:
+        if self.bias and self.activation == "silu":
+            ops.gemm_biased_swiglu(x, self.w_gate_up, self.b_gate_up, act, ctx.arena)
+        elif self.bias:
             gate_up = ctx.arena.take((t, 2 * self.intermediate_size), ctx.dtype)
             ops.gemm(x, self.w_gate_up, gate_up)
             ops.act_mul(gate_up, act, self.activation, self.limit, bias=self.b_gate_up)
