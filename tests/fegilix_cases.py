@@ -125,6 +125,14 @@ def assert_close(rows: torch.Tensor, want: torch.Tensor, dtype: torch.dtype, wha
     assert err < limit, f"{what}: relative error {err:.3g} (limit {limit})"
 
 
+class _Scratch:
+    def __init__(self, device) -> None:
+        self.device = device
+
+    def take(self, shape, dtype):
+        return torch.full(tuple(shape), float("nan"), dtype=dtype, device=self.device)
+
+
 class FakeStep:
     """The fields of a step that the recurrent references and kernels read."""
 
@@ -135,6 +143,8 @@ class FakeStep:
         self.num_seqs = len(query_lens)
         self.cu_query_lens = torch.tensor(cu, dtype=torch.int32, device=device)
         self.state_slots = torch.tensor(slots, dtype=torch.int32, device=device)
+        self.max_query_len = max(query_lens, default=0)
+        self.arena = _Scratch(device)
 
 
 def gelu_tanh(z: float) -> float:

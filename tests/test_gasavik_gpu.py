@@ -116,6 +116,23 @@ def test_gate_kernels(dtype) -> None:
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, width, per_head, gate_per_head, f32_in", [(1, 512, False, False, True), (2, 1000, True, False, True),
+                                                                           (1, 4096, False, False, True), (3, 515, False, True, False)])
+def test_norm_and_gate_of_wide_rows(dtype, heads, width, per_head, gate_per_head, f32_in) -> None:
+    """Rows of 512 values or more (all heads normed together) take a CTA each."""
+    from tinyserve_b200.kernels import ops
+
+    t = 9
+    x = _rand(t, heads, width, seed=1, dtype=torch.float32 if f32_in else dtype)
+    weight = (1 + _rand(heads * width if per_head else width, seed=2, scale=0.1)).to(dtype)
+    wide = _rand(t, 8 + (heads if gate_per_head else heads * width), seed=3, dtype=dtype)
+    a, b = torch.empty(t, heads * width, dtype=dtype, device="cuda"), torch.empty(t, heads * width, dtype=dtype, device="cuda")
+    ops.head_norm_gate(x, weight, per_head, wide[:, 8:], True, 1e-5, a, gate_per_head=gate_per_head)
+    refs.head_norm_gate(x, weight, per_head, wide[:, 8:], True, 1e-5, b, gate_per_head=gate_per_head)
+    torch.testing.assert_close(a.float(), b.float(), **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows, inter, k", [(1, 64, 128), (3, 48, 96), (8, 512, 256), (16, 1024, 1024), (29, 96, 64), (40, 96, 64),
                                             (300, 1024, 256), (700, 2048, 512), (2048, 3072, 1024), (5, 20, 36), (260, 200, 72)])
 def test_feed_forward_product_with_biases(dtype, rows, inter, k) -> None:
@@ -164,6 +181,63 @@ def test_linear_scan_kernels(dtype, heads, d, dv) -> None:
             torch.testing.assert_close(outs[0], outs[1], atol=1e-3, rtol=1e-4)
             torch.testing.assert_close(states[0][slots], states[1][slots], atol=1e-3, rtol=1e-4)
             assert states[0][[3, 7]].isnan().all() and (states[0][slots, :extra] == 0).all()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("seg_len, scratch", [(None, None), (2, None), (5, None), (16, None), (64, None), (2, 40_000), (None, 1)])
+@pytest.mark.parametrize("heads, d, dv", [(2, 16, 16), (1, 40, 70), (2, 64, 32)])
+def test_linear_scan_in_segments(dtype, seg_len, scratch, heads, d, dv, monkeypatch) -> None:
+    """Long portions cut into segments that run side by side, beside short ones and single tokens, against the
+    token-by-token reference: the segment lengths the kernel chooses itself (portions just below and above the bound
+    and a multiple of both lengths), forced short ones (edges everywhere), a scratch bound that lengthens the
+    segments, and one that leaves a single segment. A decay close to 1 and one close to 0, so that what the first
+    tokens wrote is still seen after the last segment, or gone at once; then a second step from the state."""
+    from tinyserve_b200.kernels import ops
+
+    if seg_len is not None:
+        monkeypatch.setattr(ops, "LINEAR_SCAN_SEGMENT_TOKENS", seg_len)
+        monkeypatch.setattr(ops, "LINEAR_SCAN_SEGMENT_MIN_TOKENS", 2)
+    if scratch is not None:
+        monkeypatch.setattr(ops, "LINEAR_SCAN_SEGMENT_SCRATCH_BYTES", scratch)
+    lens, slots = ([255, 1, 257, 64, 384, 129, 2], [4, 0, 6, 2, 5, 1, 7]) if seg_len is None else ([1, 37, 2, 16, 65, 3], [4, 0, 6, 2, 5, 1])
+    t, width, extra = sum(lens), heads * d * dv, 3
+    for mode in ("bonus", "decay"):
+        states = []
+        for _ in range(2):
+            st = torch.full((9, width + extra), float("nan"), device="cuda")
+            st[slots] = 0.0
+            states.append(st)
+        for phase in range(2):
+            q, k = _rand(t, heads * d, seed=1 + phase, dtype=dtype), _rand(t, heads * d, seed=3 + phase, dtype=dtype)
+            v = _rand(t, heads * dv, seed=5 + phase, dtype=dtype)
+            w_pre, w0, u = _rand(t, heads * d, seed=7 + phase) - 3.0, _rand(heads * d, seed=9) - 1.0, _rand(heads * d, seed=10)
+            w0[: d // 2] = 2.0                                   # channels that forget at once beside ones that keep
+            decay = torch.linspace(0.05, 0.9995, heads).cuda() if heads > 1 else torch.tensor([0.999]).cuda()
+            step = FakeStep(lens, slots, device="cuda")
+            outs = []
+            for impl, st in zip((ops, refs), states):
+                out = torch.full((t, heads, dv), float("nan"), device="cuda")
+                if mode == "bonus":
+                    impl.linear_scan_bonus(q, k, v, w_pre, w0, u, st[:, extra:], step, heads, d, dv, out)
+                else:
+                    impl.linear_scan_decay(q, k, v, decay, st[:, extra:], step, heads, d, dv, out)
+                outs.append(out)
+            ops.check_device_errors()
+            assert not outs[0].isnan().any()
+            scale = float(outs[1].abs().max())
+            torch.testing.assert_close(outs[0], outs[1], atol=2e-5 * scale, rtol=1e-4)
+            torch.testing.assert_close(states[0][slots], states[1][slots], atol=2e-5 * float(states[1][slots].abs().max()), rtol=1e-4)
+            assert states[0][[3, 8]].isnan().all() and (states[0][slots, :extra] == 0).all()
+
+
+def test_linear_scan_segment_choice() -> None:
+    from tinyserve_b200.kernels import ops
+
+    assert ops.linear_scan_segments(255, 1, 8, 128, 128) == (0, 1)
+    assert ops.linear_scan_segments(2048, 1, 2, 128, 64) == (64, 32)
+    assert ops.linear_scan_segments(2048, 8, 64, 64, 64) == (128, 16)
+    seg, n = ops.linear_scan_segments(8192, 16, 64, 128, 128)       # 64 MB of states a segment: the bound allows 4
+    assert n == 4 and seg % 16 == 0 and seg * n >= 8192
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

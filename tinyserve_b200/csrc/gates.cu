@@ -111,6 +111,50 @@ __global__ void head_norm_gate_kernel(const IN* __restrict__ x, const T* __restr
   }
 }
 
+// The same for wide rows (all heads normed together, say): a CTA per (token, head), the row's sum of squares
+// through shared memory.
+template <typename IN, typename T>
+__global__ void __launch_bounds__(256) head_norm_gate_wide_kernel(const IN* __restrict__ x, const T* __restrict__ weight,
+                                                                  int weight_head_stride, const T* __restrict__ gate,
+                                                                  int gate_stride, T* __restrict__ out, int heads, int width,
+                                                                  int normalise, float eps, int gate_per_head, int gate_silu) {
+  __shared__ float parts[8];
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x, t = row / heads, h = row - t * heads;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const IN* xr = x + (size_t)row * width;
+  float rstd = 1.f;
+  if (normalise) {
+    float ss = 0.f;
+    for (int c = tid; c < width; c += 256) {
+      const float v = to_float(xr[c]);
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) parts[warp] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) ss += parts[w];
+    rstd = rsqrtf(ss / (float)width + eps);
+  }
+  float head_gate = 1.f;
+  if (gate && gate_per_head) {
+    const float z = to_float(gate[(size_t)t * gate_stride + h]);
+    head_gate = gate_silu ? z * sigmoidf(z) : sigmoidf(z);
+  }
+  for (int c = tid; c < width; c += 256) {
+    float v = to_float(xr[c]) * rstd * head_gate;
+    if (weight) v *= to_float(weight[h * weight_head_stride + c]);
+    if (gate && !gate_per_head) {
+      const float z = to_float(gate[(size_t)t * gate_stride + h * width + c]);
+      v *= gate_silu ? z * sigmoidf(z) : sigmoidf(z);
+    }
+    out[(size_t)row * width + c] = from_float<T>(v);
+  }
+}
+
 }  // namespace ts
 
 using namespace ts;
@@ -179,6 +223,18 @@ extern "C" int ts_head_norm_gate(const void* x, int x_is_f32, const void* weight
                                  cudaStream_t stream) {
   const size_t warps = (size_t)num_tokens * heads;
   if (warps == 0) return 0;
+  if (width >= 512) {      // a CTA per row
+    const int rows = (int)warps;
+    if (dtype == TS_DTYPE_F32)
+      return launch(head_norm_gate_wide_kernel<float, float>, rows, 256, 0, stream, (const float*)x, (const float*)weight,
+                    weight_head_stride, (const float*)gate, gate_stride, (float*)out, heads, width, normalise, eps, gate_per_head, gate_silu);
+    if (dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
+    if (x_is_f32)
+      return launch(head_norm_gate_wide_kernel<float, bf16>, rows, 256, 0, stream, (const float*)x, (const bf16*)weight,
+                    weight_head_stride, (const bf16*)gate, gate_stride, (bf16*)out, heads, width, normalise, eps, gate_per_head, gate_silu);
+    return launch(head_norm_gate_wide_kernel<bf16, bf16>, rows, 256, 0, stream, (const bf16*)x, (const bf16*)weight,
+                  weight_head_stride, (const bf16*)gate, gate_stride, (bf16*)out, heads, width, normalise, eps, gate_per_head, gate_silu);
+  }
   const int threads = 128;
   const int b = (int)((warps * 32 + threads - 1) / threads);
   if (dtype == TS_DTYPE_F32)

@@ -13,7 +13,17 @@
 // keeps RPT elements of S in registers. Four loader warps stage the next chunk of tokens in shared
 // memory as 32-bit values (activations, decays) while the compute warps walk the current one. The
 // parts of a token's read-out (one per compute warp) wait in shared memory until the chunk is done.
-// Prompt portions and single decoded tokens are the same kernel.
+// Prompt portions and single decoded tokens are the same kernel; a step in which no request brings more
+// than one chunk of tokens (decoding) is launched without loader warps, and the compute warps stage the
+// chunk themselves.
+//
+// A long portion is cut into segments that run side by side (SCAN_LOCAL, SCAN_FINAL): the state after a
+// segment is diag(P) S_before + L, where L is what the segment's tokens leave behind from a zero state and
+// P the product of its decays (per key channel, exp(-sum_t exp(w_pre_t + w_0)), or decay_h^tokens). One
+// launch runs every segment but a request's last from zero and stores L; a small kernel walks a request's
+// segments in order and leaves each one's starting state in L's place; a last launch runs every segment
+// from its starting state, writes the read-outs, and the request's last segment stores the slot. Twice the
+// multiply-adds, but the chain is two segments long instead of the whole portion. All of it 32-bit.
 //
 // Also here: the token shift in front of the time mixing, out_m = h + (h_prev - h) * mu_m for
 // several mixes m, where h_prev of a request's first token of the step comes from its state slot
@@ -26,8 +36,9 @@ namespace ts {
 constexpr int LIN_MAX_KEY_DIM = 256;
 constexpr int LIN_LOADER_WARPS = 4;
 constexpr int LIN_LOADS = 8;
-constexpr int LIN_RPT = 32;
+constexpr int LIN_RPT = 16;
 constexpr int MODE_BONUS = 0, MODE_DECAY = 1;
+constexpr int SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_FINAL = 2;
 
 __device__ __forceinline__ float siluf(float z) { return z / (1.f + expf(-z)); }
 
@@ -44,9 +55,13 @@ struct LinScanArgs {
   int H, d, dv;
   float* out;                       // [T, H, dv]
   int W, CH;
+  int loader_warps;                 // LIN_LOADER_WARPS, or 0 when every request's tokens fit one chunk
+  int seg_len, max_segs;            // segmented: tokens per segment, segments per request in the grid
+  float* seg_state;                 // segmented: [num_seqs * max_segs, H * d * dv]
+  float* seg_decay;                 // segmented, MODE_BONUS: [num_seqs * max_segs, H * d] products of the decays
 };
 
-template <typename T, int MODE>
+template <typename T, int MODE, int PASS>
 __global__ void linear_scan_kernel(LinScanArgs a) {
   extern __shared__ __align__(16) float sm[];
   constexpr int RPT = LIN_RPT;
@@ -55,14 +70,25 @@ __global__ void linear_scan_kernel(LinScanArgs a) {
   const int dpad = W * RPT;
   const int buf_floats = CH * (NARR * dpad + 32);
   float* part = sm + 2 * buf_floats;            // [CH][W][32]
-  const int b = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * 32;
+  const int b = PASS == SCAN_WHOLE ? blockIdx.x : blockIdx.x / a.max_segs;
+  const int seg = PASS == SCAN_WHOLE ? 0 : blockIdx.x - b * a.max_segs;
+  const int h = blockIdx.y, c0 = blockIdx.z * 32;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pdl_trigger();
   pdl_wait();
-  const int start = a.cu_q[b], end = a.cu_q[b + 1];
+  int start = a.cu_q[b], end = a.cu_q[b + 1];
   if (end <= start) return;
+  bool last_seg = true;
+  if (PASS != SCAN_WHOLE) {
+    const int nsegs = (end - start + a.seg_len - 1) / a.seg_len;
+    last_seg = seg == nsegs - 1;
+    if (seg >= nsegs || (PASS == SCAN_LOCAL && last_seg)) return;
+    start += seg * a.seg_len;
+    end = min(end, start + a.seg_len);
+  }
   const int chunks = (end - start + CH - 1) / CH;
   const bool loader = warp >= W;
+  const bool own_loads = a.loader_warps == 0;    // one chunk a request: the compute warps stage it themselves
   const T* qp = (const T*)a.q;
   const T* kp = (const T*)a.k;
   const T* vp = (const T*)a.v;
@@ -73,7 +99,7 @@ __global__ void linear_scan_kernel(LinScanArgs a) {
     float* w_s = k_s + CH * dpad;                       // MODE_BONUS only
     float* v_s = q_s + NARR * CH * dpad;
     const int t0 = start + c * CH, nt = min(CH, end - t0);
-    const int lt = tid - W * 32, ln = LIN_LOADER_WARPS * 32;
+    const int lt = own_loads ? tid : tid - W * 32, ln = (own_loads ? W : LIN_LOADER_WARPS) * 32;
     for (int base = lt; base < nt * dpad; base += ln * LIN_LOADS) {
       float qv[LIN_LOADS], kv[LIN_LOADS], wv[LIN_LOADS];
 #pragma unroll
@@ -112,23 +138,29 @@ __global__ void linear_scan_kernel(LinScanArgs a) {
   const int col = c0 + lane;
   const bool col_ok = col < dv;
   float* S = a.state + (size_t)slot * a.state_stride + (size_t)h * d * dv;
+  float* S_seg = PASS == SCAN_WHOLE ? nullptr : a.seg_state + ((size_t)blockIdx.x * H + h) * d * dv;
+  const float* S_in = PASS == SCAN_FINAL ? S_seg : S;
+  float* S_out = PASS == SCAN_LOCAL ? S_seg : S;
   const int r0 = warp * RPT;
   float s[RPT], u[MODE == MODE_BONUS ? RPT : 1];
   float decay = 1.f;
   if (!loader) {
 #pragma unroll
-    for (int i = 0; i < RPT; ++i) s[i] = (r0 + i < d && col_ok) ? S[(size_t)(r0 + i) * dv + col] : 0.f;
+    for (int i = 0; i < RPT; ++i) s[i] = (PASS != SCAN_LOCAL && r0 + i < d && col_ok) ? S_in[(size_t)(r0 + i) * dv + col] : 0.f;
     if (MODE == MODE_BONUS) {
 #pragma unroll
       for (int i = 0; i < RPT; ++i) u[i] = (r0 + i < d) ? a.bonus[h * d + r0 + i] : 0.f;
     } else {
       decay = a.decay[h];
     }
-  } else {
-    load_chunk(0);
   }
+  if (loader || own_loads) load_chunk(0);
   __syncthreads();
   for (int c = 0; c < chunks; ++c) {
+    if (own_loads && c > 0) {       // not expected (the host saw a shorter step): still every chunk is staged
+      load_chunk(c);
+      __syncthreads();
+    }
     if (loader) {
       if (c + 1 < chunks) load_chunk(c + 1);
     } else {
@@ -153,33 +185,87 @@ __global__ void linear_scan_kernel(LinScanArgs a) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const float kv = kx[e] * vv;
-              const float seen = fmaf(u[4 * i + e], kv, s[4 * i + e]);
-              if (e & 1) o1 = fmaf(seen, qx[e], o1); else o0 = fmaf(seen, qx[e], o0);
+              if (PASS != SCAN_LOCAL) {
+                const float seen = fmaf(u[4 * i + e], kv, s[4 * i + e]);
+                if (e & 1) o1 = fmaf(seen, qx[e], o1); else o0 = fmaf(seen, qx[e], o0);
+              }
               s[4 * i + e] = fmaf(wx[e], s[4 * i + e], kv);
             }
           } else {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               s[4 * i + e] = fmaf(decay, s[4 * i + e], kx[e] * vv);
-              if (e & 1) o1 = fmaf(s[4 * i + e], qx[e], o1); else o0 = fmaf(s[4 * i + e], qx[e], o0);
+              if (PASS != SCAN_LOCAL) {
+                if (e & 1) o1 = fmaf(s[4 * i + e], qx[e], o1); else o0 = fmaf(s[4 * i + e], qx[e], o0);
+              }
             }
           }
         }
-        part[(tok * W + warp) * 32 + lane] = o0 + o1;
+        if (PASS != SCAN_LOCAL) part[(tok * W + warp) * 32 + lane] = o0 + o1;
       }
-      if (W > 1) asm volatile("bar.sync 1, %0;" ::"r"(W * 32) : "memory"); else __syncwarp();
-      for (int tok = warp; tok < nt; tok += W) {
-        float o = 0.f;
-        for (int w = 0; w < W; ++w) o += part[(tok * W + w) * 32 + lane];
-        if (col_ok) a.out[((size_t)(t0 + tok) * H + h) * dv + col] = o;
+      if (PASS != SCAN_LOCAL) {
+        if (W > 1) asm volatile("bar.sync 1, %0;" ::"r"(W * 32) : "memory"); else __syncwarp();
+        for (int tok = warp; tok < nt; tok += W) {
+          float o = 0.f;
+          for (int w = 0; w < W; ++w) o += part[(tok * W + w) * 32 + lane];
+          if (col_ok) a.out[((size_t)(t0 + tok) * H + h) * dv + col] = o;
+        }
       }
     }
     __syncthreads();
   }
-  if (loader) return;
+  if (loader || (PASS == SCAN_FINAL && !last_seg)) return;
 #pragma unroll
   for (int i = 0; i < RPT; ++i)
-    if (r0 + i < d && col_ok) S[(size_t)(r0 + i) * dv + col] = s[i];
+    if (r0 + i < d && col_ok) S_out[(size_t)(r0 + i) * dv + col] = s[i];
+}
+
+// The product of a segment's decays per key channel, exp(-sum_t exp(w_pre_t + w_0)), for every segment but a
+// request's last. A thread per channel; grid (request * max_segs + segment, blocks of 128 channels).
+__global__ void linear_scan_seg_decay_kernel(LinScanArgs a) {
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.x / a.max_segs, seg = blockIdx.x - b * a.max_segs;
+  const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+  int start = a.cu_q[b];
+  const int end = a.cu_q[b + 1];
+  const int nsegs = (end - start + a.seg_len - 1) / a.seg_len;
+  if (seg >= nsegs - 1 || ch >= a.H * a.d) return;
+  start += seg * a.seg_len;
+  const float bias = a.w_bias[ch];
+  float sum = 0.f;
+  for (int t = start; t < start + a.seg_len; ++t) sum += expf(a.w_pre[(size_t)t * a.w_stride + ch] + bias);
+  a.seg_decay[(size_t)blockIdx.x * a.H * a.d + ch] = expf(-sum);
+}
+
+// A request's segments in order: seg_state[segment] holds what the segment leaves from a zero state and
+// receives the state the segment starts from (the slot's for the first). A thread per state element; grid
+// (request, head, blocks of 256 elements).
+template <int MODE>
+__global__ void linear_scan_combine_kernel(LinScanArgs a) {
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int idx = blockIdx.z * blockDim.x + threadIdx.x;
+  const int start = a.cu_q[b], end = a.cu_q[b + 1];
+  const int nsegs = (end - start + a.seg_len - 1) / a.seg_len;
+  const int per_head = a.d * a.dv;
+  if (nsegs <= 0 || idx >= per_head) return;
+  const int r = idx / a.dv;
+  float s = a.state[(size_t)a.state_slots[b] * a.state_stride + (size_t)h * per_head + idx];
+  float p_const = 1.f;
+  if (MODE == MODE_DECAY && nsegs > 1) {
+    const float dec = a.decay[h];
+    for (int t = 0; t < a.seg_len; ++t) p_const *= dec;
+  }
+  for (int seg = 0; seg < nsegs; ++seg) {
+    const size_t row = (size_t)b * a.max_segs + seg;
+    float* p = a.seg_state + (row * a.H + h) * per_head + idx;
+    const bool more = seg + 1 < nsegs;
+    const float left = more ? *p : 0.f;
+    *p = s;
+    if (more) s = fmaf(MODE == MODE_BONUS ? a.seg_decay[row * a.H * a.d + h * a.d + r] : p_const, s, left);
+  }
 }
 
 // ------------------------------------------------------------------- token shift
@@ -231,27 +317,44 @@ static int lin_allow_smem(K kern, size_t smem, size_t& allowed) {
   return e;
 }
 
-template <typename T, int MODE>
-static int launch_linear(const LinScanArgs& a, dim3 grid, cudaStream_t stream) {
+template <typename T, int MODE, int PASS>
+static int launch_linear_pass(const LinScanArgs& a, dim3 grid, cudaStream_t stream) {
   const int dpad = a.W * LIN_RPT;
   const int narr = MODE == MODE_BONUS ? 3 : 2;
   const size_t smem = sizeof(float) * (2 * (size_t)a.CH * (narr * dpad + 32) + (size_t)a.CH * a.W * 32);
-  auto kern = linear_scan_kernel<T, MODE>;
+  auto kern = linear_scan_kernel<T, MODE, PASS>;
   static size_t allowed = 0;
   if (int e = lin_allow_smem(kern, smem, allowed)) return e;
-  return launch(kern, grid, (a.W + LIN_LOADER_WARPS) * 32, smem, stream, a);
+  return launch(kern, grid, (a.W + a.loader_warps) * 32, smem, stream, a);
+}
+
+template <typename T, int MODE>
+static int launch_linear(const LinScanArgs& a, int num_seqs, cudaStream_t stream) {
+  const int col_blocks = (a.dv + 31) / 32;
+  if (a.max_segs <= 1) return launch_linear_pass<T, MODE, SCAN_WHOLE>(a, dim3(num_seqs, a.H, col_blocks), stream);
+  const dim3 grid(num_seqs * a.max_segs, a.H, col_blocks);
+  if (MODE == MODE_BONUS)
+    if (int e = launch(linear_scan_seg_decay_kernel, dim3(num_seqs * a.max_segs, (a.H * a.d + 127) / 128), 128, 0, stream, a)) return e;
+  if (int e = launch_linear_pass<T, MODE, SCAN_LOCAL>(a, grid, stream)) return e;
+  if (int e = launch(linear_scan_combine_kernel<MODE>, dim3(num_seqs, a.H, (a.d * a.dv + 255) / 256), 256, 0, stream, a)) return e;
+  return launch_linear_pass<T, MODE, SCAN_FINAL>(a, grid, stream);
 }
 
 // mode 0: bonus read-out with a decay per key channel and token; mode 1: constant decay per head, SiLU on q, k, v.
+// max_segs > 1 cuts every request's tokens into segments of seg_len (max_segs * seg_len covers the longest) that
+// run side by side (max_query_len = the most tokens any request brings): seg_state [num_seqs * max_segs, heads * d * dv] and, for mode 0, seg_decay
+// [num_seqs * max_segs, heads * d] are scratch.
 extern "C" int ts_linear_scan(int mode, const void* q, int q_stride, const void* k, int k_stride, const void* v,
                               int v_stride, const float* w_pre, int w_stride, const float* w_bias, const float* bonus,
                               const float* decay, float* state, int state_stride, const int* cu_q,
                               const int* state_slots, int num_seqs, int heads, int d, int dv, float* out, int dtype,
+                              int max_query_len, int seg_len, int max_segs, float* seg_state, float* seg_decay,
                               cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
   if (d <= 0 || dv <= 0 || d > LIN_MAX_KEY_DIM) return TS_ERR_UNSUPPORTED;
   if (mode == MODE_BONUS ? (!w_pre || !w_bias || !bonus) : (mode != MODE_DECAY || !decay)) return TS_ERR_BAD_ARGUMENT;
   if (dtype != TS_DTYPE_F32 && dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
+  if (max_segs > 1 && (seg_len <= 0 || !seg_state || (mode == MODE_BONUS && !seg_decay))) return TS_ERR_BAD_ARGUMENT;
   LinScanArgs a;
   a.q = q; a.q_stride = q_stride; a.k = k; a.k_stride = k_stride; a.v = v; a.v_stride = v_stride;
   a.w_pre = w_pre; a.w_stride = w_stride; a.w_bias = w_bias; a.bonus = bonus; a.decay = decay;
@@ -259,10 +362,11 @@ extern "C" int ts_linear_scan(int mode, const void* q, int q_stride, const void*
   a.H = heads; a.d = d; a.dv = dv; a.out = out;
   a.W = (d + LIN_RPT - 1) / LIN_RPT;
   a.CH = a.W * LIN_RPT <= 128 ? 16 : 8;
-  dim3 grid(num_seqs, heads, (dv + 31) / 32);
+  a.loader_warps = (max_query_len > 0 && max_query_len <= a.CH) ? 0 : LIN_LOADER_WARPS;
+  a.seg_len = seg_len; a.max_segs = max_segs > 1 ? max_segs : 1; a.seg_state = seg_state; a.seg_decay = seg_decay;
   if (mode == MODE_BONUS)
-    return dtype == TS_DTYPE_F32 ? launch_linear<float, MODE_BONUS>(a, grid, stream) : launch_linear<bf16, MODE_BONUS>(a, grid, stream);
-  return dtype == TS_DTYPE_F32 ? launch_linear<float, MODE_DECAY>(a, grid, stream) : launch_linear<bf16, MODE_DECAY>(a, grid, stream);
+    return dtype == TS_DTYPE_F32 ? launch_linear<float, MODE_BONUS>(a, num_seqs, stream) : launch_linear<bf16, MODE_BONUS>(a, num_seqs, stream);
+  return dtype == TS_DTYPE_F32 ? launch_linear<float, MODE_DECAY>(a, num_seqs, stream) : launch_linear<bf16, MODE_DECAY>(a, num_seqs, stream);
 }
 
 extern "C" int ts_token_shift_mix(const void* x, int x_stride, const void* mu, int num_mixes, float* state,

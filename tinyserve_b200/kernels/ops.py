@@ -43,7 +43,8 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_stream_sum": [_vp, _vp, _vp, _vp, _vp, _f, _f, _f, _f, _i, _vp, _f, _vp, _i, _i, _i, _vp],
     "ts_add_bias": [_vp, _vp, _i, _i, _i, _vp],
     "ts_tanh": [_vp, _c.c_size_t, _i, _vp],
-    "ts_linear_scan": [_i, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp],
+    "ts_linear_scan": [_i, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _i, _vp, _vp,
+                       _vp],
     "ts_token_shift_mix": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _vp, _i, _vp],
     "ts_softcap": [_vp, _c.c_size_t, _f, _vp],
     "ts_head_norm_gate": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
@@ -1317,13 +1318,43 @@ def _linear_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w
     elif decay.shape != (heads,):
         raise KernelError("linear_scan: one decay per head")
     state_ptr, state_stride = _state_rows(state, heads * d * dv, "linear_scan")
+    seg_len, max_segs = linear_scan_segments(ctx.max_query_len, ctx.num_seqs, heads, d, dv)
+    seg_state = seg_decay = None
+    if max_segs > 1:
+        seg_state = ctx.arena.take((ctx.num_seqs * max_segs, heads * d * dv), torch.float32)
+        if mode == 0:
+            seg_decay = ctx.arena.take((ctx.num_seqs * max_segs, heads * d), torch.float32)
     _check(_fn("ts_linear_scan")(
         mode, q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
         None if w_pre is None else w_pre.data_ptr(), 0 if w_pre is None else w_pre.stride(0),
         _opt(w_bias, "w_bias", torch.float32), _opt(bonus, "bonus", torch.float32), _opt(decay, "decay", torch.float32),
         state_ptr, state_stride, _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
         _dev(ctx.state_slots, "state_slots", torch.int32), ctx.num_seqs, heads, d, dv,
-        _dev(out, "out", torch.float32), _code(dt), _stream()), "linear_scan")
+        _dev(out, "out", torch.float32), _code(dt), int(ctx.max_query_len), seg_len, max_segs,
+        None if seg_state is None else seg_state.data_ptr(), None if seg_decay is None else seg_decay.data_ptr(), _stream()),
+        "linear_scan", kernels=1 if max_segs <= 1 else (4 if mode == 0 else 3))
+
+
+# A portion of this many tokens or more is cut into segments that run side by side.
+LINEAR_SCAN_SEGMENT_MIN_TOKENS = 256
+LINEAR_SCAN_SEGMENT_SCRATCH_BYTES = 256 << 20
+LINEAR_SCAN_SEGMENT_TOKENS: int | None = None    # a fixed segment length instead of the choice below (tests)
+
+
+def linear_scan_segments(max_query_len: int, num_seqs: int, heads: int, d: int, dv: int) -> tuple[int, int]:
+    """``(tokens per segment, segments per request)`` for a step whose longest portion has ``max_query_len`` tokens;
+    one segment = the plain scan. Segments of 64 tokens while the machine has room for more CTAs than the
+    requests, heads and column blocks give, of 128 beyond; longer ones when the segments' states would not fit
+    the scratch bound."""
+    if max_query_len < LINEAR_SCAN_SEGMENT_MIN_TOKENS:
+        return 0, 1
+    ctas = num_seqs * heads * ((dv + 31) // 32)
+    seg_len = LINEAR_SCAN_SEGMENT_TOKENS or (64 if ctas * ((max_query_len + 127) // 128) < 2 * 148 else 128)
+    most = max(1, LINEAR_SCAN_SEGMENT_SCRATCH_BYTES // (4 * heads * d * dv * max(1, num_seqs)))
+    if (max_query_len + seg_len - 1) // seg_len > most:
+        seg_len = ((max_query_len + most - 1) // most + 15) // 16 * 16
+    max_segs = (max_query_len + seg_len - 1) // seg_len
+    return (seg_len, max_segs) if max_segs > 1 else (0, 1)
 
 
 def token_shift_mix(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, ctx: Any, out: torch.Tensor) -> None:
