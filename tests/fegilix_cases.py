@@ -144,6 +144,7 @@ class FakeStep:
         self.cu_query_lens = torch.tensor(cu, dtype=torch.int32, device=device)
         self.state_slots = torch.tensor(slots, dtype=torch.int32, device=device)
         self.max_query_len = max(query_lens, default=0)
+        self.query_lens = list(query_lens)
         self.arena = _Scratch(device)
 
 

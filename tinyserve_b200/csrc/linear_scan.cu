@@ -233,8 +233,17 @@ __global__ void linear_scan_seg_decay_kernel(LinScanArgs a) {
   if (seg >= nsegs - 1 || ch >= a.H * a.d) return;
   start += seg * a.seg_len;
   const float bias = a.w_bias[ch];
+  const float* wp = a.w_pre + (size_t)start * a.w_stride + ch;
   float sum = 0.f;
-  for (int t = start; t < start + a.seg_len; ++t) sum += expf(a.w_pre[(size_t)t * a.w_stride + ch] + bias);
+  int t = 0;
+  for (; t + 8 <= a.seg_len; t += 8) {           // eight loads in flight
+    float x[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = wp[(size_t)(t + j) * a.w_stride];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sum += expf(x[j] + bias);
+  }
+  for (; t < a.seg_len; ++t) sum += expf(wp[(size_t)t * a.w_stride] + bias);
   a.seg_decay[(size_t)blockIdx.x * a.H * a.d + ch] = expf(-sum);
 }
 
@@ -258,13 +267,24 @@ __global__ void linear_scan_combine_kernel(LinScanArgs a) {
     const float dec = a.decay[h];
     for (int t = 0; t < a.seg_len; ++t) p_const *= dec;
   }
-  for (int seg = 0; seg < nsegs; ++seg) {
-    const size_t row = (size_t)b * a.max_segs + seg;
-    float* p = a.seg_state + (row * a.H + h) * per_head + idx;
-    const bool more = seg + 1 < nsegs;
-    const float left = more ? *p : 0.f;
-    *p = s;
-    if (more) s = fmaf(MODE == MODE_BONUS ? a.seg_decay[row * a.H * a.d + h * a.d + r] : p_const, s, left);
+  const size_t seg_stride = (size_t)a.H * per_head;
+  float* p0 = a.seg_state + ((size_t)b * a.max_segs * a.H + h) * per_head + idx;
+  const float* d0 = a.seg_decay + (size_t)b * a.max_segs * a.H * a.d + h * a.d + r;     // MODE_BONUS only
+  for (int s0 = 0; s0 < nsegs; s0 += 8) {        // eight segments' loads in flight, then the chain
+    float left[8], pp[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool more = s0 + j + 1 < nsegs;
+      left[j] = more ? p0[(size_t)(s0 + j) * seg_stride] : 0.f;
+      pp[j] = !more ? 0.f : MODE == MODE_BONUS ? d0[(size_t)(s0 + j) * a.H * a.d] : p_const;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (s0 + j < nsegs) {
+        p0[(size_t)(s0 + j) * seg_stride] = s;
+        if (s0 + j + 1 < nsegs) s = fmaf(pp[j], s, left[j]);
+      }
+    }
   }
 }
 
