@@ -89,7 +89,7 @@ DESIGNS = {"fegilix": fegilix_config, "guzovik": guzovik_config, "gasavik": gasa
 NEW_OPS = ["post_norm_add_rms_norm", "latent_prepare", "latent_attention", "bmm", "transpose01", "moe_route_from", "moe_route", "moe_gemm",
            "moe_combine", "gemm_gated", "hc_mix_norm", "hc_collapse", "act_mul", "softcap", "head_norm_gate", "mlstm_scan", "delta_scan",
            "causal_conv_silu", "qkv_prepare", "linear_scan_bonus", "linear_scan_decay", "token_shift_mix", "embed_pos_norm",
-           "stream_sum", "add_bias", "tanh_", "act_mul_gather"]
+           "stream_sum", "add_bias", "tanh_", "act_mul_gather", "gemm_biased_swiglu"]
 OLD_OPS = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_write", "paged_attention",
            "decode_attention_fused", "gemm", "gemm_swiglu", "gemm_to_stream", "gemm_normed", "sample"]
 
@@ -169,6 +169,8 @@ class DesignBench(Bench):
             """(bytes, flops) of one call."""
             if name in ("gemm", "gemm_swiglu", "gemm_to_stream", "gemm_gated"):
                 return nbytes(a[0], a[1], a[2]), 2.0 * a[0].shape[0] * a[1].shape[0] * a[1].shape[1]
+            if name == "gemm_biased_swiglu":      # x, the gate and up rows, the biases, the result
+                return nbytes(a[0], a[1], a[2], a[3]), 2.0 * a[0].shape[0] * a[1].shape[0] * a[1].shape[1]
             if name == "bmm":
                 return nbytes(a[0], a[1], a[2]), 2.0 * a[0].shape[0] * a[0].shape[1] * a[0].shape[2] * a[1].shape[2]
             if name == "moe_gemm":            # the matrices of the experts that have rows, the rows in and out
