@@ -434,6 +434,29 @@ def test_configurations_drawn_at_random(seed, tmp_path) -> None:
             _check(got, reqs, want, dtype, f"seed {seed}, schedule {n}: {json.dumps(cfg)[:300]}")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompts_whose_scans_run_in_segments(dtype, tmp_path) -> None:
+    """Prompts of several hundred tokens: the linear scans of a long portion run in segments. Whole, in long and
+    short portions (one just above the bound), decoded at the end, and mixed with a short request."""
+    import copy
+
+    from tinyserve_b200.kernels import ops
+    from tinyserve_b200.model import DecoderModel
+
+    cfg = copy.deepcopy(CONFIGS["D"][0])
+    cfg["max_positions"] = 720
+    folder = write_model(tmp_path, cfg, 31)
+    reqs = {"long": random_prompt(700, cfg["vocab"], 41), "mid": random_prompt(300, cfg["vocab"], 42), "short": random_prompt(9, cfg["vocab"], 43)}
+    assert ops.linear_scan_segments(700, 1, 2, 64, 64)[1] > 1 and ops.linear_scan_segments(257, 3, 2, 64, 64)[1] > 1
+    want = {rid: plain_oracle(folder, toks) for rid, toks in reqs.items()}
+    model = DecoderModel.from_folder(folder, dtype, "cuda")
+    plans = [cases.whole("long", reqs["long"]), cases.tail_decoded("long", reqs["long"], 20),
+             cases.portions("long", reqs["long"], 1, sizes=(300, 257, 2, 100)), cases.mixed(reqs, 2)]
+    for n, steps in enumerate(plans):
+        got, _ = run_steps(model, 16, steps, cases.max_live_tokens(steps))
+        _check(got, {rid: reqs[rid] for rid in got}, want, dtype, f"long prompts, schedule {n}")
+
+
 def test_batch_mates_pages_and_slots_do_not_matter(folders, oracle) -> None:
     """float32: a request's logits alone, beside others, and again on the pages and in the slot that another
     request has just given back, agree to rounding."""

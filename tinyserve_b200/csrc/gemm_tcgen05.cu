@@ -58,6 +58,9 @@ __device__ __forceinline__ void drain_tile(uint32_t tmem_acc, int row, int M, in
       if (row < M) {
         bf16* dst = (bf16*)out + (size_t)row * N + n0 + c * 32;
         float f[32];
+        [[maybe_unused]] float bg[8], bu[8];
+        [[maybe_unused]] const bool bias_vec = SWIGLU == GATED_BIASED_SILU && n0 + c * 32 + 32 <= N && N % 8 == 0 &&
+                                               (((uintptr_t)act_bias) & 15) == 0;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           if constexpr (SWIGLU == GATED_GELU_TANH) {
@@ -68,9 +71,30 @@ __device__ __forceinline__ void drain_tile(uint32_t tmem_acc, int row, int M, in
             asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * fmaf(0.044715f * z * z, z, z)));
             f[j] = 0.5f * z * (1.f + th) * __uint_as_float(u[j]);
           } else if constexpr (SWIGLU == GATED_BIASED_SILU) {
-            const int col = min(n0 + c * 32 + j, N - 1);          // columns past the edge are computed and not stored
-            const float gv = __uint_as_float(g[j]) + to_float(act_bias[col]);
-            f[j] = __fdividef(gv, 1.f + __expf(-gv)) * (__uint_as_float(u[j]) + to_float(act_bias[N + col]));
+            if (j % 8 == 0) {      // the biases of eight columns: two 16-byte reads where the chunk lies inside the row
+              const int col0 = n0 + c * 32 + j;
+              if (bias_vec) {
+                const uint4 pg = *reinterpret_cast<const uint4*>(act_bias + col0);
+                const uint4 pu = *reinterpret_cast<const uint4*>(act_bias + N + col0);
+                const uint32_t wg[4] = {pg.x, pg.y, pg.z, pg.w}, wu[4] = {pu.x, pu.y, pu.z, pu.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  bg[2 * e] = __uint_as_float(wg[e] << 16);
+                  bg[2 * e + 1] = __uint_as_float(wg[e] & 0xffff0000u);
+                  bu[2 * e] = __uint_as_float(wu[e] << 16);
+                  bu[2 * e + 1] = __uint_as_float(wu[e] & 0xffff0000u);
+                }
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const int col = min(col0 + e, N - 1);           // columns past the edge are computed and not stored
+                  bg[e] = to_float(act_bias[col]);
+                  bu[e] = to_float(act_bias[N + col]);
+                }
+              }
+            }
+            const float gv = __uint_as_float(g[j]) + bg[j % 8];
+            f[j] = __fdividef(gv, 1.f + __expf(-gv)) * (__uint_as_float(u[j]) + bu[j % 8]);
           } else if constexpr (SWIGLU == GATED_CLAMPED_SWISH) {
             const float gv = fminf(__uint_as_float(g[j]), act_limit);
             const float uv = fminf(fmaxf(__uint_as_float(u[j]), -act_limit), act_limit);
