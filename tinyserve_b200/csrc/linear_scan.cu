@@ -62,7 +62,7 @@ struct LinScanArgs {
 };
 
 template <typename T, int MODE, int PASS>
-__global__ void linear_scan_kernel(LinScanArgs a) {
+__device__ __forceinline__ void linear_scan_body(const LinScanArgs& a) {
   extern __shared__ __align__(16) float sm[];
   constexpr int RPT = LIN_RPT;
   constexpr int NARR = MODE == MODE_BONUS ? 3 : 2;
@@ -220,6 +220,15 @@ __global__ void linear_scan_kernel(LinScanArgs a) {
     if (r0 + i < d && col_ok) S_out[(size_t)(r0 + i) * dv + col] = s[i];
 }
 
+template <typename T, int MODE>
+__global__ void linear_scan_kernel(LinScanArgs a) { linear_scan_body<T, MODE, SCAN_WHOLE>(a); }
+
+// The passes over segments: 80 registers a thread (a few spilled words outside the token loop) let three CTAs of
+// eight warps share an SM instead of two: 9 to 25 % off a pass at key sizes 64 and 128. The one-launch form, which
+// single tokens take, keeps the registers it asks for.
+template <typename T, int MODE, int PASS>
+__global__ void __maxnreg__(80) linear_scan_segment_kernel(LinScanArgs a) { linear_scan_body<T, MODE, PASS>(a); }
+
 // The product of a segment's decays per key channel, exp(-sum_t exp(w_pre_t + w_0)), for every segment but a
 // request's last. A thread per channel; grid (request * max_segs + segment, blocks of 128 channels).
 __global__ void linear_scan_seg_decay_kernel(LinScanArgs a) {
@@ -342,10 +351,16 @@ static int launch_linear_pass(const LinScanArgs& a, dim3 grid, cudaStream_t stre
   const int dpad = a.W * LIN_RPT;
   const int narr = MODE == MODE_BONUS ? 3 : 2;
   const size_t smem = sizeof(float) * (2 * (size_t)a.CH * (narr * dpad + 32) + (size_t)a.CH * a.W * 32);
-  auto kern = linear_scan_kernel<T, MODE, PASS>;
   static size_t allowed = 0;
-  if (int e = lin_allow_smem(kern, smem, allowed)) return e;
-  return launch(kern, grid, (a.W + a.loader_warps) * 32, smem, stream, a);
+  if constexpr (PASS == SCAN_WHOLE) {
+    auto kern = linear_scan_kernel<T, MODE>;
+    if (int e = lin_allow_smem(kern, smem, allowed)) return e;
+    return launch(kern, grid, (a.W + a.loader_warps) * 32, smem, stream, a);
+  } else {
+    auto kern = linear_scan_segment_kernel<T, MODE, PASS>;
+    if (int e = lin_allow_smem(kern, smem, allowed)) return e;
+    return launch(kern, grid, (a.W + a.loader_warps) * 32, smem, stream, a);
+  }
 }
 
 template <typename T, int MODE>
