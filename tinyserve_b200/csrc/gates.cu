@@ -155,6 +155,26 @@ __global__ void __launch_bounds__(256) head_norm_gate_wide_kernel(const IN* __re
   }
 }
 
+// RMSNorm of rows that lie `x_stride` elements apart (a column slice of a wider product): out[r] =
+// dt(x[r] / sqrt(mean(x[r]^2) + eps) * weight), 32-bit and rounded once. A CTA per row.
+template <typename T>
+__global__ void rms_norm_rows_kernel(const T* __restrict__ x, long long x_stride, const T* __restrict__ weight, float eps,
+                                     T* __restrict__ out, int width) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const T* xr = x + (size_t)blockIdx.x * x_stride;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = to_float(xr[c]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    out[(size_t)blockIdx.x * width + c] = from_float<T>(to_float(xr[c]) * rstd * to_float(weight[c]));
+}
+
 }  // namespace ts
 
 using namespace ts;
@@ -246,4 +266,18 @@ extern "C" int ts_head_norm_gate(const void* x, int x_is_f32, const void* weight
                   weight_head_stride, (const bf16*)gate, gate_stride, (bf16*)out, num_tokens, heads, width, normalise, eps, gate_per_head, gate_silu);
   return launch(head_norm_gate_kernel<bf16, bf16>, b, threads, 0, stream, (const bf16*)x, (const bf16*)weight,
                 weight_head_stride, (const bf16*)gate, gate_stride, (bf16*)out, num_tokens, heads, width, normalise, eps, gate_per_head, gate_silu);
+}
+
+extern "C" int ts_rms_norm_rows(const void* x, long long x_stride, const void* weight, float eps, void* out, int num_rows,
+                                int width, int dtype, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (width <= 0 || x_stride < width || !weight) return TS_ERR_BAD_ARGUMENT;
+  const int threads = width >= 512 ? 256 : width >= 128 ? 128 : 32;
+  if (dtype == TS_DTYPE_F32)
+    return launch(rms_norm_rows_kernel<float>, num_rows, threads, 0, stream, (const float*)x, x_stride, (const float*)weight, eps,
+                  (float*)out, width);
+  if (dtype == TS_DTYPE_BF16)
+    return launch(rms_norm_rows_kernel<bf16>, num_rows, threads, 0, stream, (const bf16*)x, x_stride, (const bf16*)weight, eps,
+                  (bf16*)out, width);
+  return TS_ERR_BAD_ARGUMENT;
 }

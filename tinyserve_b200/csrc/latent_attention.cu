@@ -100,6 +100,8 @@ struct LatentAttnArgs {
   int table_width, num_seqs, heads, rank, rot, page_size;
   float scale_log2;
   int window;              // 0: every earlier position
+  const float* sinks;      // [H] or null: a logit per head (natural base, not scaled) that joins the softmax's
+                           // denominator and has no value
   int tokens_per_cta, heads_per_cta;
 };
 
@@ -216,7 +218,14 @@ __global__ void __launch_bounds__(LA_THREADS) latent_attention_kernel(LatentAttn
       if (!live[i]) continue;
       const int r = pass0 + warp + i * LA_WARPS;
       const int tt = r / nh, hh = r - tt * nh;
-      const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+      float den = l[i], keep = 1.f;
+      if (a.sinks) {
+        const float sk = a.sinks[h0 + hh] * 1.4426950408889634f;
+        const float m_new = fmaxf(m[i], sk);
+        keep = exp2f(m[i] - m_new);                   // m = -inf gives 0
+        den = den * keep + exp2f(sk - m_new);
+      }
+      const float inv = den > 0.f ? keep / den : 0.f;
 #pragma unroll
       for (int j = 0; j < RJ; ++j) {
         const int col = lane + 32 * j;
@@ -493,7 +502,14 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
     const size_t orow = (size_t)(row0 + t0 + tt) * a.heads + h0 + hh;
     const float l = half ? l_b : l_a, m = half ? m_b : m_a;
     if (sp.splits == 1) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      float den = l, keep = 1.f;
+      if (a.sinks) {
+        const float sk = a.sinks[h0 + hh] * 1.4426950408889634f;
+        const float m_new = fmaxf(m, sk);
+        keep = exp2f(m - m_new);                      // m = -inf gives 0
+        den = den * keep + exp2f(sk - m_new);
+      }
+      const float inv = den > 0.f ? keep / den : 0.f;
       bf16* out = (bf16*)a.out + orow * R;
 #pragma unroll
       for (int j = 0; j < NB; ++j) {
@@ -516,8 +532,9 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(Lat
 }
 
 // out[row, :] = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s over the key ranges of a row.
+// With sinks, head (row % heads) adds 2^(sink log2(e) - M) to the denominator.
 __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, bf16* __restrict__ out,
-                                    int splits, int R) {
+                                    int splits, int R, const float* __restrict__ sinks, int heads) {
   pdl_trigger();
   pdl_wait();
   const size_t row = blockIdx.x;
@@ -525,6 +542,11 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const fl
   float mm = -INFINITY;
   for (int s = 0; s < splits; ++s) mm = fmaxf(mm, ml[2 * s]);
   float den = 0.f;
+  if (sinks) {
+    const float sk = sinks[row % heads] * 1.4426950408889634f;
+    mm = fmaxf(mm, sk);
+    den = exp2f(sk - mm);
+  }
   for (int s = 0; s < splits; ++s) den += ml[2 * s] == -INFINITY ? 0.f : ml[2 * s + 1] * exp2f(ml[2 * s] - mm);
   const float inv = den > 0.f ? 1.f / den : 0.f;
   for (int c = threadIdx.x; c < R; c += blockDim.x) {
@@ -590,13 +612,15 @@ extern "C" int ts_latent_attention_mma_takes(int rank, int rot) {
 extern "C" int ts_latent_attention(const void* q, void* out, const void* cache, const int* block_tables, int table_width,
                                    const int* cu_q, const int* ctx_lens, int num_seqs, int max_query_len, int heads,
                                    int rank, int rot, int page_size, float scale, int window, int dtype, int use_mma,
-                                   int splits, float* part_acc, float* part_ml, int num_tokens, cudaStream_t stream) {
+                                   int splits, float* part_acc, float* part_ml, int num_tokens, const float* sinks,
+                                   cudaStream_t stream) {
   if (num_seqs <= 0 || max_query_len <= 0) return 0;
   if (heads <= 0 || rank <= 0 || rank > 512 || rot < 0 || page_size <= 0 || window < 0) return TS_ERR_BAD_ARGUMENT;
   LatentAttnArgs a;
   a.q = q; a.out = out; a.cache = cache; a.block_tables = block_tables; a.table_width = table_width;
   a.cu_q = cu_q; a.ctx_lens = ctx_lens; a.num_seqs = num_seqs; a.heads = heads; a.rank = rank; a.rot = rot;
   a.page_size = page_size; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
+  a.sinks = sinks;
   if (dtype == TS_DTYPE_BF16 && use_mma && ts_latent_attention_mma_takes(rank, rot) &&
       (((uintptr_t)q | (uintptr_t)cache | (uintptr_t)out) & 15) == 0) {
     if (splits < 1 || (splits > 1 && (max_query_len != 1 || !part_acc || !part_ml))) return TS_ERR_BAD_ARGUMENT;
@@ -612,7 +636,7 @@ extern "C" int ts_latent_attention(const void* q, void* out, const void* cache, 
     else st = launch_latent_mma<32>(a, sp, max_query_len, stream);
     if (st != 0 || splits == 1) return st;
     return launch(latent_merge_kernel, num_tokens * heads, 128, 0, stream, (const float*)part_acc, (const float*)part_ml,
-                  (bf16*)out, splits, rank);
+                  (bf16*)out, splits, rank, sinks, heads);
   }
   // 32 rows a CTA where the step has them: 8 heads of 4 tokens (a single token: 8 heads)
   a.heads_per_cta = heads < 8 ? heads : 8;

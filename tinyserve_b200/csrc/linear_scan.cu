@@ -7,6 +7,9 @@
 //    bonus u per key channel: o = (S + diag(u) k v^T)^T r; then S <- diag(w) S + k v^T.
 //  * MODE_DECAY (linear attention with a constant decay per head): q, k, v pass SiLU;
 //    S <- decay_h S + k v^T; o = S^T q (the read-out sees the current token's write).
+//  * MODE_GATED (gated linear attention): a decay per key channel and token,
+//    alpha = sigmoid(z)^(1/tau) = exp(logsigmoid(z) / tau) with z = w_pre + w_0; q is multiplied by a constant;
+//    S <- diag(alpha) S + k v^T; o = S^T q (the read-out sees the current token's write).
 //
 // Work split as in the other recurrent kernels: a CTA owns (request, head, block of 32 value
 // columns); compute warp w owns key rows [w * RPT, (w + 1) * RPT) and lane c column c, so a thread
@@ -19,7 +22,7 @@
 //
 // A long portion is cut into segments that run side by side (SCAN_LOCAL, SCAN_FINAL): the state after a
 // segment is diag(P) S_before + L, where L is what the segment's tokens leave behind from a zero state and
-// P the product of its decays (per key channel, exp(-sum_t exp(w_pre_t + w_0)), or decay_h^tokens). One
+// P the product of its decays (per key channel, exp(-sum_t exp(w_pre_t + w_0)) or exp(sum_t logsigmoid(z_t) / tau), or decay_h^tokens). One
 // launch runs every segment but a request's last from zero and stores L; a small kernel walks a request's
 // segments in order and leaves each one's starting state in L's place; a last launch runs every segment
 // from its starting state, writes the read-outs, and the request's last segment stores the slot. Twice the
@@ -37,17 +40,20 @@ constexpr int LIN_MAX_KEY_DIM = 256;
 constexpr int LIN_LOADER_WARPS = 4;
 constexpr int LIN_LOADS = 8;
 constexpr int LIN_RPT = 16;
-constexpr int MODE_BONUS = 0, MODE_DECAY = 1;
+constexpr int MODE_BONUS = 0, MODE_DECAY = 1, MODE_GATED = 2;
 constexpr int SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_FINAL = 2;
 
 __device__ __forceinline__ float siluf(float z) { return z / (1.f + expf(-z)); }
+// log(sigmoid(z)) = min(z, 0) - log(1 + exp(-|z|))
+__device__ __forceinline__ float logsigmoidf(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
 struct LinScanArgs {
   const void* q; int q_stride;      // [T, H * d] rows q_stride apart (r of the time mixing)
   const void* k; int k_stride;      // [T, H * d]
   const void* v; int v_stride;      // [T, H * dv]
-  const float* w_pre; int w_stride; // MODE_BONUS: [T, H * d] decay pre-activations
-  const float* w_bias;              // MODE_BONUS: [H * d]
+  const float* w_pre; int w_stride; // MODE_BONUS, MODE_GATED: [T, H * d] decay pre-activations
+  const float* w_bias;              // MODE_BONUS, MODE_GATED: [H * d]
+  float inv_tau, q_scale;           // MODE_GATED: 1 / tau of the decay, and the constant on q
   const float* bonus;               // MODE_BONUS: [H * d]
   const float* decay;               // MODE_DECAY: [H]
   float* state; int state_stride;   // [slots, H * d * dv]
@@ -58,14 +64,15 @@ struct LinScanArgs {
   int loader_warps;                 // LIN_LOADER_WARPS, or 0 when every request's tokens fit one chunk
   int seg_len, max_segs;            // segmented: tokens per segment, segments per request in the grid
   float* seg_state;                 // segmented: [num_seqs * max_segs, H * d * dv]
-  float* seg_decay;                 // segmented, MODE_BONUS: [num_seqs * max_segs, H * d] products of the decays
+  float* seg_decay;                 // segmented, MODE_BONUS, MODE_GATED: [num_seqs * max_segs, H * d] products of the decays
 };
 
 template <typename T, int MODE, int PASS>
 __device__ __forceinline__ void linear_scan_body(const LinScanArgs& a) {
   extern __shared__ __align__(16) float sm[];
   constexpr int RPT = LIN_RPT;
-  constexpr int NARR = MODE == MODE_BONUS ? 3 : 2;
+  constexpr bool CHANNEL_DECAY = MODE == MODE_BONUS || MODE == MODE_GATED;
+  constexpr int NARR = CHANNEL_DECAY ? 3 : 2;
   const int W = a.W, CH = a.CH, d = a.d, dv = a.dv, H = a.H;
   const int dpad = W * RPT;
   const int buf_floats = CH * (NARR * dpad + 32);
@@ -96,7 +103,7 @@ __device__ __forceinline__ void linear_scan_body(const LinScanArgs& a) {
   auto load_chunk = [&](int c) {
     float* q_s = sm + (c & 1) * buf_floats;
     float* k_s = q_s + CH * dpad;
-    float* w_s = k_s + CH * dpad;                       // MODE_BONUS only
+    float* w_s = k_s + CH * dpad;                       // a decay per key channel only
     float* v_s = q_s + NARR * CH * dpad;
     const int t0 = start + c * CH, nt = min(CH, end - t0);
     const int lt = own_loads ? tid : tid - W * 32, ln = (own_loads ? W : LIN_LOADER_WARPS) * 32;
@@ -109,7 +116,7 @@ __device__ __forceinline__ void linear_scan_body(const LinScanArgs& a) {
         const bool ok = idx < nt * dpad && r < d;
         qv[u] = ok ? to_float(qp[(size_t)(t0 + tok) * a.q_stride + h * d + r]) : 0.f;
         kv[u] = ok ? to_float(kp[(size_t)(t0 + tok) * a.k_stride + h * d + r]) : 0.f;
-        if (MODE == MODE_BONUS) wv[u] = ok ? a.w_pre[(size_t)(t0 + tok) * a.w_stride + h * d + r] + a.w_bias[h * d + r] : 0.f;
+        if (CHANNEL_DECAY) wv[u] = ok ? a.w_pre[(size_t)(t0 + tok) * a.w_stride + h * d + r] + a.w_bias[h * d + r] : 0.f;
       }
 #pragma unroll
       for (int u = 0; u < LIN_LOADS; ++u) {
@@ -118,6 +125,10 @@ __device__ __forceinline__ void linear_scan_body(const LinScanArgs& a) {
           if (MODE == MODE_DECAY) {
             q_s[idx] = siluf(qv[u]);
             k_s[idx] = siluf(kv[u]);
+          } else if (MODE == MODE_GATED) {
+            q_s[idx] = qv[u] * a.q_scale;
+            k_s[idx] = kv[u];
+            w_s[idx] = expf(logsigmoidf(wv[u]) * a.inv_tau);
           } else {
             q_s[idx] = qv[u];
             k_s[idx] = kv[u];
@@ -150,7 +161,7 @@ __device__ __forceinline__ void linear_scan_body(const LinScanArgs& a) {
     if (MODE == MODE_BONUS) {
 #pragma unroll
       for (int i = 0; i < RPT; ++i) u[i] = (r0 + i < d) ? a.bonus[h * d + r0 + i] : 0.f;
-    } else {
+    } else if (MODE == MODE_DECAY) {
       decay = a.decay[h];
     }
   }
@@ -191,6 +202,16 @@ __device__ __forceinline__ void linear_scan_body(const LinScanArgs& a) {
               }
               s[4 * i + e] = fmaf(wx[e], s[4 * i + e], kv);
             }
+          } else if (MODE == MODE_GATED) {
+            const float4 ww = w4[i];
+            const float wx[4] = {ww.x, ww.y, ww.z, ww.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              s[4 * i + e] = fmaf(wx[e], s[4 * i + e], kx[e] * vv);
+              if (PASS != SCAN_LOCAL) {
+                if (e & 1) o1 = fmaf(s[4 * i + e], qx[e], o1); else o0 = fmaf(s[4 * i + e], qx[e], o0);
+              }
+            }
           } else {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -229,8 +250,10 @@ __global__ void linear_scan_kernel(LinScanArgs a) { linear_scan_body<T, MODE, SC
 template <typename T, int MODE, int PASS>
 __global__ void __maxnreg__(80) linear_scan_segment_kernel(LinScanArgs a) { linear_scan_body<T, MODE, PASS>(a); }
 
-// The product of a segment's decays per key channel, exp(-sum_t exp(w_pre_t + w_0)), for every segment but a
-// request's last. A thread per channel; grid (request * max_segs + segment, blocks of 128 channels).
+// The product of a segment's decays per key channel, exp(-sum_t exp(w_pre_t + w_0)) (MODE_GATED:
+// exp(sum_t logsigmoid(w_pre_t + w_0) / tau)), for every segment but a request's last. A thread per channel; grid
+// (request * max_segs + segment, blocks of 128 channels).
+template <int MODE>
 __global__ void linear_scan_seg_decay_kernel(LinScanArgs a) {
   pdl_trigger();
   pdl_wait();
@@ -250,9 +273,12 @@ __global__ void linear_scan_seg_decay_kernel(LinScanArgs a) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) x[j] = wp[(size_t)(t + j) * a.w_stride];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) sum += expf(x[j] + bias);
+    for (int j = 0; j < 8; ++j) sum += MODE == MODE_GATED ? -logsigmoidf(x[j] + bias) * a.inv_tau : expf(x[j] + bias);
   }
-  for (; t < a.seg_len; ++t) sum += expf(wp[(size_t)t * a.w_stride] + bias);
+  for (; t < a.seg_len; ++t) {
+    const float z = wp[(size_t)t * a.w_stride] + bias;
+    sum += MODE == MODE_GATED ? -logsigmoidf(z) * a.inv_tau : expf(z);
+  }
   a.seg_decay[(size_t)blockIdx.x * a.H * a.d + ch] = expf(-sum);
 }
 
@@ -278,14 +304,14 @@ __global__ void linear_scan_combine_kernel(LinScanArgs a) {
   }
   const size_t seg_stride = (size_t)a.H * per_head;
   float* p0 = a.seg_state + ((size_t)b * a.max_segs * a.H + h) * per_head + idx;
-  const float* d0 = a.seg_decay + (size_t)b * a.max_segs * a.H * a.d + h * a.d + r;     // MODE_BONUS only
+  const float* d0 = a.seg_decay + (size_t)b * a.max_segs * a.H * a.d + h * a.d + r;     // a decay per key channel only
   for (int s0 = 0; s0 < nsegs; s0 += 8) {        // eight segments' loads in flight, then the chain
     float left[8], pp[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const bool more = s0 + j + 1 < nsegs;
       left[j] = more ? p0[(size_t)(s0 + j) * seg_stride] : 0.f;
-      pp[j] = !more ? 0.f : MODE == MODE_BONUS ? d0[(size_t)(s0 + j) * a.H * a.d] : p_const;
+      pp[j] = !more ? 0.f : MODE != MODE_DECAY ? d0[(size_t)(s0 + j) * a.H * a.d] : p_const;
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -349,7 +375,7 @@ static int lin_allow_smem(K kern, size_t smem, size_t& allowed) {
 template <typename T, int MODE, int PASS>
 static int launch_linear_pass(const LinScanArgs& a, dim3 grid, cudaStream_t stream) {
   const int dpad = a.W * LIN_RPT;
-  const int narr = MODE == MODE_BONUS ? 3 : 2;
+  const int narr = MODE == MODE_DECAY ? 2 : 3;
   const size_t smem = sizeof(float) * (2 * (size_t)a.CH * (narr * dpad + 32) + (size_t)a.CH * a.W * 32);
   static size_t allowed = 0;
   if constexpr (PASS == SCAN_WHOLE) {
@@ -368,39 +394,43 @@ static int launch_linear(const LinScanArgs& a, int num_seqs, cudaStream_t stream
   const int col_blocks = (a.dv + 31) / 32;
   if (a.max_segs <= 1) return launch_linear_pass<T, MODE, SCAN_WHOLE>(a, dim3(num_seqs, a.H, col_blocks), stream);
   const dim3 grid(num_seqs * a.max_segs, a.H, col_blocks);
-  if (MODE == MODE_BONUS)
-    if (int e = launch(linear_scan_seg_decay_kernel, dim3(num_seqs * a.max_segs, (a.H * a.d + 127) / 128), 128, 0, stream, a)) return e;
+  if (MODE != MODE_DECAY)
+    if (int e = launch(linear_scan_seg_decay_kernel<MODE>, dim3(num_seqs * a.max_segs, (a.H * a.d + 127) / 128), 128, 0, stream, a)) return e;
   if (int e = launch_linear_pass<T, MODE, SCAN_LOCAL>(a, grid, stream)) return e;
   if (int e = launch(linear_scan_combine_kernel<MODE>, dim3(num_seqs, a.H, (a.d * a.dv + 255) / 256), 256, 0, stream, a)) return e;
   return launch_linear_pass<T, MODE, SCAN_FINAL>(a, grid, stream);
 }
 
-// mode 0: bonus read-out with a decay per key channel and token; mode 1: constant decay per head, SiLU on q, k, v.
+// mode 0: bonus read-out with a decay per key channel and token; mode 1: constant decay per head, SiLU on q, k, v;
+// mode 2: decay sigmoid(w_pre + w_bias)^(inv_tau) per key channel and token, q times q_scale, read-out after the write.
 // max_segs > 1 cuts every request's tokens into segments of seg_len (max_segs * seg_len covers the longest) that
-// run side by side (max_query_len = the most tokens any request brings): seg_state [num_seqs * max_segs, heads * d * dv] and, for mode 0, seg_decay
+// run side by side (max_query_len = the most tokens any request brings): seg_state [num_seqs * max_segs, heads * d * dv] and, for modes 0 and 2, seg_decay
 // [num_seqs * max_segs, heads * d] are scratch.
 extern "C" int ts_linear_scan(int mode, const void* q, int q_stride, const void* k, int k_stride, const void* v,
                               int v_stride, const float* w_pre, int w_stride, const float* w_bias, const float* bonus,
                               const float* decay, float* state, int state_stride, const int* cu_q,
                               const int* state_slots, int num_seqs, int heads, int d, int dv, float* out, int dtype,
                               int max_query_len, int seg_len, int max_segs, float* seg_state, float* seg_decay,
-                              cudaStream_t stream) {
+                              float inv_tau, float q_scale, cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
   if (d <= 0 || dv <= 0 || d > LIN_MAX_KEY_DIM) return TS_ERR_UNSUPPORTED;
-  if (mode == MODE_BONUS ? (!w_pre || !w_bias || !bonus) : (mode != MODE_DECAY || !decay)) return TS_ERR_BAD_ARGUMENT;
+  if (mode == MODE_BONUS ? (!w_pre || !w_bias || !bonus) : mode == MODE_GATED ? (!w_pre || !w_bias || !(inv_tau > 0.f))
+                                                             : (mode != MODE_DECAY || !decay)) return TS_ERR_BAD_ARGUMENT;
   if (dtype != TS_DTYPE_F32 && dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
-  if (max_segs > 1 && (seg_len <= 0 || !seg_state || (mode == MODE_BONUS && !seg_decay))) return TS_ERR_BAD_ARGUMENT;
+  if (max_segs > 1 && (seg_len <= 0 || !seg_state || (mode != MODE_DECAY && !seg_decay))) return TS_ERR_BAD_ARGUMENT;
   LinScanArgs a;
   a.q = q; a.q_stride = q_stride; a.k = k; a.k_stride = k_stride; a.v = v; a.v_stride = v_stride;
   a.w_pre = w_pre; a.w_stride = w_stride; a.w_bias = w_bias; a.bonus = bonus; a.decay = decay;
   a.state = state; a.state_stride = state_stride; a.cu_q = cu_q; a.state_slots = state_slots;
-  a.H = heads; a.d = d; a.dv = dv; a.out = out;
+  a.H = heads; a.d = d; a.dv = dv; a.out = out; a.inv_tau = inv_tau; a.q_scale = q_scale;
   a.W = (d + LIN_RPT - 1) / LIN_RPT;
   a.CH = a.W * LIN_RPT <= 128 ? 16 : 8;
   a.loader_warps = (max_query_len > 0 && max_query_len <= a.CH) ? 0 : LIN_LOADER_WARPS;
   a.seg_len = seg_len; a.max_segs = max_segs > 1 ? max_segs : 1; a.seg_state = seg_state; a.seg_decay = seg_decay;
   if (mode == MODE_BONUS)
     return dtype == TS_DTYPE_F32 ? launch_linear<float, MODE_BONUS>(a, num_seqs, stream) : launch_linear<bf16, MODE_BONUS>(a, num_seqs, stream);
+  if (mode == MODE_GATED)
+    return dtype == TS_DTYPE_F32 ? launch_linear<float, MODE_GATED>(a, num_seqs, stream) : launch_linear<bf16, MODE_GATED>(a, num_seqs, stream);
   return dtype == TS_DTYPE_F32 ? launch_linear<float, MODE_DECAY>(a, num_seqs, stream) : launch_linear<bf16, MODE_DECAY>(a, num_seqs, stream);
 }
 

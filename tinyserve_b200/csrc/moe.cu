@@ -2,14 +2,19 @@
 //
 //   route    a warp per token picks the `top` largest of its E router logits (32-bit; ties go to
 //            the lower index), soft-maxes the picked logits alone, and takes a place in each picked
-//            expert's queue (an atomic counter per expert);
+//            expert's queue (an atomic counter per expert). A second rule (RouteRule::scored) soft-maxes
+//            ALL outputs first, picks by score + correction inside the best groups of neighbouring
+//            outputs only, and weights the picks by their scores over the picks' sum, times a constant;
+//            the last outputs may be identity experts, which have no matrices and no queue: their
+//            picks carry the token's own input to the combine step;
 //   plan     one thread turns the counters into the experts' row ranges of the sorted order and
 //            into a list of row tiles (expert, first row), and clears the counters for the next step;
 //   scatter  every (token, pick) learns its row of the sorted order; the row learns its token;
 //   products tile by tile over that list: act[row, :] = silu(x[token] Wgate_e^T) * (x[token] Wup_e^T)
 //            (the token's row of x is fetched through the list, nothing is copied), then
 //            y[row, :] = act[row, :] Wdown_e^T;
-//   combine  out[token] = sum_j weight_j y[row_j] (+ the shared expert's output), 32-bit, rounded once.
+//   combine  out[token] = sum_j weight_j y[row_j] (+ the shared expert's output, optionally times the sigmoid
+//            of a gate logit per token), 32-bit, rounded once; an identity pick's y is the token's input.
 //
 // A row's sums run over K in index order whatever its tile holds, so a token's result does not
 // depend on which other tokens share the step or on the order in which the queue places were taken.
@@ -23,16 +28,60 @@ namespace ts {
 // ------------------------------------------------------------------------- route
 // One token by one warp: picks, weights, and a place in each picked expert's queue (`counts` may be
 // in shared memory).
+// How a token's picks and weights follow from its router outputs.
+struct RouteRule {
+  int scored;               // 0: the largest logits, weighted by the softmax over the picks alone
+                            // 1: softmax over all outputs; picks by score + correction within the best groups;
+                            //    weights = scores of the picks / (their sum + 1e-20) * scale
+  int real;                 // outputs that are experts with matrices (the first ones); the rest are identity experts
+  int groups, keep;         // scored: equal groups of neighbouring outputs, of which the `keep` best may be picked from
+  float scale;              // scored: constant on the weights
+  const float* correction;  // scored: [E] added to the scores for the choice only, or null
+  int ld;                   // floats between two tokens' rows of router outputs
+};
+
+// One token by one warp: picks, weights, and a place in each picked expert's queue (`counts` may be
+// in shared memory). A pick of an identity expert (id >= rule.real) takes no place (-1).
 __device__ __forceinline__ void route_token(const float* __restrict__ z, int t, int lane, int E, int top, int* __restrict__ ids,
-                                            float* __restrict__ weights, int* __restrict__ place, int* counts) {
+                                            float* __restrict__ weights, int* __restrict__ place, int* counts,
+                                            const RouteRule& rule) {
+  float zmax = 0.f, inv_sum = 1.f;
+  unsigned allowed = 0xffffffffu;          // bit g: group g may be picked from
+  int group_size = E;
+  if (rule.scored) {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+    zmax = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(z[e] - zmax);
+    inv_sum = 1.f / warp_sum(sum);
+    if (rule.groups > 1) {
+      // lane g: the best choice score of group g, then its rank among the groups (value down, index up)
+      group_size = E / rule.groups;
+      float best = -INFINITY;
+      if (lane < rule.groups)
+        for (int e = lane * group_size; e < (lane + 1) * group_size; ++e)
+          best = fmaxf(best, expf(z[e] - zmax) * inv_sum + (rule.correction ? rule.correction[e] : 0.f));
+      int rank = 0;
+      for (int g = 0; g < rule.groups; ++g) {
+        const float other = __shfl_sync(0xffffffffu, best, g);
+        rank += (other > best || (other == best && g < lane)) ? 1 : 0;
+      }
+      allowed = __ballot_sync(0xffffffffu, lane < rule.groups && rank < rule.keep);
+    }
+  }
   float prev_v = INFINITY, my_v = -INFINITY;
-  int prev_e = -1, my_e = 0;
+  int prev_e = -1, my_e = -1;
   for (int j = 0; j < top; ++j) {
     // the largest element that comes after the pick before in the order (value down, index up)
     float bv = -INFINITY;
     int be = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
-      const float v = z[e];
+      float v = z[e];
+      if (rule.scored) {
+        v = expf(v - zmax) * inv_sum + (rule.correction ? rule.correction[e] : 0.f);
+        if (!((allowed >> (e / group_size)) & 1u)) continue;
+      }
       const bool after = (v < prev_v) || (v == prev_v && e > prev_e);
       if (after && (v > bv || (v == bv && e < be))) { bv = v; be = e; }
     }
@@ -46,25 +95,31 @@ __device__ __forceinline__ void route_token(const float* __restrict__ z, int t, 
     prev_v = bv;
     prev_e = be;
   }
-  const float head = __shfl_sync(0xffffffffu, my_v, 0);
-  const float p = lane < top ? expf(my_v - head) : 0.f;
+  const bool picked = lane < top && my_e >= 0 && my_e < E;   // fewer finite candidates than picks: the pick is dropped
+  float p;
+  if (rule.scored) {
+    p = picked ? expf(z[my_e] - zmax) * inv_sum : 0.f;        // the score itself, without the correction
+  } else {
+    const float head = __shfl_sync(0xffffffffu, my_v, 0);
+    p = lane < top ? expf(my_v - head) : 0.f;
+  }
   const float sum = warp_sum(p);
   if (lane < top) {
-    const bool real = my_e >= 0 && my_e < E;       // fewer finite logits than picks: the pick is dropped
-    const int e = real ? my_e : 0;
+    const int e = picked ? my_e : 0;
+    const float w = rule.scored ? p / (sum + 1e-20f) * rule.scale : p / sum;
     ids[(size_t)t * top + lane] = e;
-    weights[(size_t)t * top + lane] = real ? p / sum : 0.f;
-    place[(size_t)t * top + lane] = atomicAdd(&counts[e], 1);
+    weights[(size_t)t * top + lane] = picked ? w : 0.f;
+    place[(size_t)t * top + lane] = e < rule.real ? atomicAdd(&counts[e], 1) : -1;
   }
 }
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, int num_tokens, int E, int top, int* __restrict__ ids,
-                                 float* __restrict__ weights, int* __restrict__ place, int* __restrict__ counts) {
+                                 float* __restrict__ weights, int* __restrict__ place, int* __restrict__ counts, RouteRule rule) {
   pdl_trigger();
   pdl_wait();
   const int t = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
   if (t >= num_tokens) return;
-  route_token(logits + (size_t)t * E, t, lane, E, top, ids, weights, place, counts);
+  route_token(logits + (size_t)t * rule.ld, t, lane, E, top, ids, weights, place, counts, rule);
 }
 
 // A step of few tokens (decoding): route, plan and scatter by ONE CTA, the queue counters in shared
@@ -78,7 +133,7 @@ __global__ void __launch_bounds__(ROUTE_SMALL_THREADS) moe_route_small_kernel(
     float* logits, int num_tokens, int E, int top, int tile_rows, int* __restrict__ ids,
     float* __restrict__ weights, int* __restrict__ place, int* __restrict__ offsets, int* __restrict__ tile_expert,
     int* __restrict__ tile_row0, int* __restrict__ num_tiles, int max_tiles, int* __restrict__ row_of,
-    int* __restrict__ token_of) {
+    int* __restrict__ token_of, RouteRule rule) {
   __shared__ int counts[ROUTE_SMALL_MAX_EXPERTS];
   __shared__ int offs[ROUTE_SMALL_MAX_EXPERTS + 1];
   pdl_trigger();
@@ -108,15 +163,16 @@ __global__ void __launch_bounds__(ROUTE_SMALL_THREADS) moe_route_small_kernel(
         for (int i = lane; i < hidden; i += 32) sum = fmaf(to_float(xr[i]), to_float(wr[i]), sum);
       }
       sum = warp_sum(sum);
-      if (lane == 0) logits[pair] = sum;
+      if (lane == 0) logits[(size_t)t * rule.ld + e] = sum;
     }
   }
   __syncthreads();
-  for (int t = warp; t < num_tokens; t += warps) route_token(logits + (size_t)t * E, t, lane, E, top, ids, weights, place, counts);
+  for (int t = warp; t < num_tokens; t += warps)
+    route_token(logits + (size_t)t * rule.ld, t, lane, E, top, ids, weights, place, counts, rule);
   __syncthreads();
   if (threadIdx.x == 0) {
     int off = 0, nt = 0;
-    for (int e = 0; e < E; ++e) {
+    for (int e = 0; e < rule.real; ++e) {
       const int c = counts[e];
       offs[e] = off;
       offsets[e] = off;
@@ -127,11 +183,15 @@ __global__ void __launch_bounds__(ROUTE_SMALL_THREADS) moe_route_small_kernel(
       }
       off += c;
     }
-    offsets[E] = off;
+    offsets[rule.real] = off;
     *num_tiles = nt;
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < num_tokens * top; idx += blockDim.x) {
+    if (place[idx] < 0) {              // an identity pick: no row of the sorted order
+      row_of[idx] = -1;
+      continue;
+    }
     const int row = offs[ids[idx]] + place[idx];
     row_of[idx] = row;
     token_of[row] = idx / top;
@@ -168,6 +228,10 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __res
   pdl_wait();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
+  if (place[idx] < 0) {                // an identity pick: no row of the sorted order
+    row_of[idx] = -1;
+    return;
+  }
   const int row = offsets[ids[idx]] + place[idx];
   row_of[idx] = row;
   token_of[row] = idx / top;
@@ -401,15 +465,19 @@ __global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __rest
 // ----------------------------------------------------------------------- combine
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ row_of, const float* __restrict__ weights,
-                                   const T* __restrict__ shared_out, T* __restrict__ out, int top, int hidden) {
+                                   const T* __restrict__ shared_out, T* __restrict__ out, int top, int hidden,
+                                   const T* __restrict__ x, const float* __restrict__ shared_gate, int gate_stride) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
+  const float sg = shared_gate ? 1.f / (1.f + expf(-shared_gate[(size_t)t * gate_stride])) : 1.f;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float v = 0.f;
-    for (int j = 0; j < top; ++j)
-      v = fmaf(weights[(size_t)t * top + j], to_float(y[(size_t)row_of[(size_t)t * top + j] * hidden + c]), v);
-    if (shared_out) v += to_float(shared_out[(size_t)t * hidden + c]);
+    for (int j = 0; j < top; ++j) {
+      const int row = row_of[(size_t)t * top + j];
+      v = fmaf(weights[(size_t)t * top + j], to_float(row >= 0 ? y[(size_t)row * hidden + c] : x[(size_t)t * hidden + c]), v);
+    }
+    if (shared_out) v = fmaf(sg, to_float(shared_out[(size_t)t * hidden + c]), v);
     out[(size_t)t * hidden + c] = from_float<T>(v);
   }
 }
@@ -418,11 +486,13 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
 // are asked for together, up to eight at a time.
 template <typename T>
 __global__ void moe_combine_vec_kernel(const T* __restrict__ y, const int* __restrict__ row_of, const float* __restrict__ weights,
-                                       const T* __restrict__ shared_out, T* __restrict__ out, int top, int hidden) {
+                                       const T* __restrict__ shared_out, T* __restrict__ out, int top, int hidden,
+                                       const T* __restrict__ x, const float* __restrict__ shared_gate, int gate_stride) {
   constexpr int VEC = Vec<T>::N;
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
+  const float sg = shared_gate ? 1.f / (1.f + expf(-shared_gate[(size_t)t * gate_stride])) : 1.f;
   const int* rows = row_of + (size_t)t * top;
   const float* wt = weights + (size_t)t * top;
   for (int c = threadIdx.x * VEC; c < hidden; c += blockDim.x * VEC) {
@@ -433,7 +503,7 @@ __global__ void moe_combine_vec_kernel(const T* __restrict__ y, const int* __res
       Vec<T> part[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u)
-        if (j0 + u < top) part[u].load(y + (size_t)rows[j0 + u] * hidden + c);
+        if (j0 + u < top) part[u].load(rows[j0 + u] >= 0 ? y + (size_t)rows[j0 + u] * hidden + c : x + (size_t)t * hidden + c);
 #pragma unroll
       for (int u = 0; u < 8; ++u)
         if (j0 + u < top) {
@@ -450,7 +520,7 @@ __global__ void moe_combine_vec_kernel(const T* __restrict__ y, const int* __res
       float f[VEC];
       sv.unpack(f);
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) acc[e] += f[e];
+      for (int e = 0; e < VEC; ++e) acc[e] = fmaf(sg, f[e], acc[e]);
     }
     Vec<T> ov;
     ov.pack(acc);
@@ -464,25 +534,40 @@ using namespace ts;
 
 extern "C" int ts_moe_tile_rows() { return SG_M; }      // both product forms use tiles of 64 rows
 
-// logits [T, E] float -> ids / weights / place [T, top]; counts [E] (zero on entry, zero again after the plan);
-// offsets [E + 1]; tile_expert / tile_row0 [max_tiles]; num_tiles [1]; row_of [T * top]; token_of [T * top].
+// The rule's arguments, checked: E outputs of which the first `real` are experts with matrices.
+static int make_rule(RouteRule& r, int E, int real, int top, int scored, int groups, int keep, float scale,
+                     const float* correction, int ld) {
+  if (E <= 0 || real <= 0 || real > E || top <= 0 || top > 32 || top > E || ld < E) return TS_ERR_BAD_ARGUMENT;
+  if (!scored && (real != E || groups > 1 || correction)) return TS_ERR_BAD_ARGUMENT;
+  if (groups < 1) groups = 1;
+  if (groups > 32 || E % groups || keep < 1 || keep > groups || (E / groups) * keep < top) return TS_ERR_BAD_ARGUMENT;
+  r.scored = scored; r.real = real; r.groups = groups; r.keep = keep; r.scale = scale; r.correction = correction; r.ld = ld;
+  return 0;
+}
+
+// logits [T, ld >= E] float -> ids / weights / place [T, top]; counts [real] (zero on entry, zero again after the plan);
+// offsets [real + 1]; tile_expert / tile_row0 [max_tiles]; num_tiles [1]; row_of [T * top]; token_of [T * top].
 // tile_rows: rows of a tile of the list (64 for the products of this file, 128 for the tcgen05 product).
-extern "C" int ts_moe_route(const float* logits, int num_tokens, int E, int top, int* ids, float* weights, int* place,
+// scored / groups / keep / scale / correction / real: see RouteRule (scored 0 wants real = E, groups <= 1).
+extern "C" int ts_moe_route(const float* logits, int ld, int num_tokens, int E, int real, int top, int scored, int groups,
+                            int keep, float scale, const float* correction, int* ids, float* weights, int* place,
                             int* counts, int* offsets, int* tile_expert, int* tile_row0, int* num_tiles, int max_tiles,
                             int* row_of, int* token_of, int tile_rows, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (tile_rows != 64 && tile_rows != 128) return TS_ERR_BAD_ARGUMENT;
+  RouteRule rule;
+  if (int e = make_rule(rule, E, real, top, scored, groups, keep, scale, correction, ld)) return e;
   const int picks = num_tokens * top;
-  const int most = picks < picks / tile_rows + E ? picks : picks / tile_rows + E;   // every tile has a row; an expert one ragged tile
-  if (E <= 0 || top <= 0 || top > 32 || top > E || max_tiles < most) return TS_ERR_BAD_ARGUMENT;
+  const int most = picks < picks / tile_rows + real ? picks : picks / tile_rows + real;   // every tile has a row; an expert one ragged tile
+  if (max_tiles < most) return TS_ERR_BAD_ARGUMENT;
   if (num_tokens <= 64 && E <= ROUTE_SMALL_MAX_EXPERTS)
     return launch(moe_route_small_kernel<float>, 1, ROUTE_SMALL_THREADS, 0, stream, (const float*)nullptr, (const float*)nullptr, 0,
                   const_cast<float*>(logits), num_tokens, E, top, tile_rows, ids, weights, place, offsets, tile_expert, tile_row0,
-                  num_tiles, max_tiles, row_of, token_of);
+                  num_tiles, max_tiles, row_of, token_of, rule);
   int st = launch(moe_route_kernel, (num_tokens * 32 + 127) / 128, 128, 0, stream, logits, num_tokens, E, top, ids,
-                  weights, place, counts);
+                  weights, place, counts, rule);
   if (st != 0) return st;
-  st = launch(moe_plan_kernel, 1, 32, 0, stream, counts, E, tile_rows, offsets, tile_expert, tile_row0, num_tiles, max_tiles);
+  st = launch(moe_plan_kernel, 1, 32, 0, stream, counts, real, tile_rows, offsets, tile_expert, tile_row0, num_tiles, max_tiles);
   if (st != 0) return st;
   const int total = num_tokens * top;
   return launch(moe_scatter_kernel, (total + 255) / 256, 256, 0, stream, (const int*)ids, (const int*)place,
@@ -490,25 +575,27 @@ extern "C" int ts_moe_route(const float* logits, int num_tokens, int E, int top,
 }
 
 // The same for a step of up to 64 tokens with the router's product inside: logits (scratch, [T, E] float) are
-// formed from x [T, hidden] and w_router [E, hidden] of `dtype` by the one CTA that routes.
+// formed from x [T, hidden] and w_router [E, hidden] of `dtype` by the one CTA that routes (the plain rule only).
 extern "C" int ts_moe_route_fused(const void* x, const void* w_router, int hidden, int dtype, float* logits, int num_tokens,
                                   int E, int top, int* ids, float* weights, int* place, int* offsets, int* tile_expert,
                                   int* tile_row0, int* num_tiles, int max_tiles, int* row_of, int* token_of, int tile_rows,
                                   cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (tile_rows != 64 && tile_rows != 128) return TS_ERR_BAD_ARGUMENT;
+  RouteRule rule;
+  if (int e = make_rule(rule, E, E, top, 0, 1, 1, 1.f, nullptr, E)) return e;
   const int picks = num_tokens * top;
   const int most = picks < picks / tile_rows + E ? picks : picks / tile_rows + E;
-  if (E <= 0 || top <= 0 || top > 32 || top > E || max_tiles < most || hidden <= 0 || !x || !w_router) return TS_ERR_BAD_ARGUMENT;
+  if (max_tiles < most || hidden <= 0 || !x || !w_router) return TS_ERR_BAD_ARGUMENT;
   if (num_tokens > 64 || E > ROUTE_SMALL_MAX_EXPERTS) return TS_ERR_UNSUPPORTED;
   if (dtype == TS_DTYPE_F32)
     return launch(moe_route_small_kernel<float>, 1, ROUTE_SMALL_THREADS, 0, stream, (const float*)x, (const float*)w_router, hidden,
                   logits, num_tokens, E, top, tile_rows, ids, weights, place, offsets, tile_expert, tile_row0, num_tiles, max_tiles,
-                  row_of, token_of);
+                  row_of, token_of, rule);
   if (dtype == TS_DTYPE_BF16)
     return launch(moe_route_small_kernel<bf16>, 1, ROUTE_SMALL_THREADS, 0, stream, (const bf16*)x, (const bf16*)w_router, hidden,
                   logits, num_tokens, E, top, tile_rows, ids, weights, place, offsets, tile_expert, tile_row0, num_tiles, max_tiles,
-                  row_of, token_of);
+                  row_of, token_of, rule);
   return TS_ERR_BAD_ARGUMENT;
 }
 
@@ -556,27 +643,30 @@ extern "C" int ts_moe_gather(const void* x, const int* token_of, void* xs, int p
   return launch(moe_gather_kernel, (int)blocks, 256, 0, stream, (const uint4*)x, token_of, (uint4*)xs, picks, pieces);
 }
 
+// x [T, hidden] (the tokens' inputs) is read for identity picks (row_of < 0) and may be null when there are none;
+// shared_gate (float, one logit per token, gate_stride floats apart) multiplies the shared output by its sigmoid.
 extern "C" int ts_moe_combine(const void* y, const int* row_of, const float* weights, const void* shared_out, void* out,
-                              int num_tokens, int top, int hidden, int dtype, cudaStream_t stream) {
+                              int num_tokens, int top, int hidden, const void* x, const float* shared_gate, int gate_stride,
+                              int dtype, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   const int vec = dtype == TS_DTYPE_F32 ? 4 : 8;
-  if (hidden % vec == 0 && (((uintptr_t)y | (uintptr_t)shared_out | (uintptr_t)out) & 15) == 0) {
+  if (hidden % vec == 0 && (((uintptr_t)y | (uintptr_t)shared_out | (uintptr_t)out | (uintptr_t)x) & 15) == 0) {
     int vthreads = 32;
     while (vthreads < 256 && vthreads * vec < hidden) vthreads <<= 1;
     if (dtype == TS_DTYPE_F32)
       return launch(moe_combine_vec_kernel<float>, num_tokens, vthreads, 0, stream, (const float*)y, row_of, weights,
-                    (const float*)shared_out, (float*)out, top, hidden);
+                    (const float*)shared_out, (float*)out, top, hidden, (const float*)x, shared_gate, gate_stride);
     if (dtype == TS_DTYPE_BF16)
       return launch(moe_combine_vec_kernel<bf16>, num_tokens, vthreads, 0, stream, (const bf16*)y, row_of, weights,
-                    (const bf16*)shared_out, (bf16*)out, top, hidden);
+                    (const bf16*)shared_out, (bf16*)out, top, hidden, (const bf16*)x, shared_gate, gate_stride);
     return TS_ERR_BAD_ARGUMENT;
   }
   if (dtype == TS_DTYPE_F32)
     return launch(moe_combine_kernel<float>, num_tokens, threads, 0, stream, (const float*)y, row_of, weights,
-                  (const float*)shared_out, (float*)out, top, hidden);
+                  (const float*)shared_out, (float*)out, top, hidden, (const float*)x, shared_gate, gate_stride);
   if (dtype == TS_DTYPE_BF16)
     return launch(moe_combine_kernel<bf16>, num_tokens, threads, 0, stream, (const bf16*)y, row_of, weights,
-                  (const bf16*)shared_out, (bf16*)out, top, hidden);
+                  (const bf16*)shared_out, (bf16*)out, top, hidden, (const bf16*)x, shared_gate, gate_stride);
   return TS_ERR_BAD_ARGUMENT;
 }

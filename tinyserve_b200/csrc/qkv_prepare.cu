@@ -4,8 +4,9 @@
 // queries go to q_out [T, heads, d], keys to k_cache [pages, kv_heads, page_size, d] and values,
 // unchanged, to v_cache [pages, kv_heads, page_size, dv] at the token's slot. q, k and v are read
 // from rows with strides of their own, so they may be parts of one merged projection. Optional
-// biases (one value per projection row) are added first. All arithmetic is 32-bit and the result
-// is rounded once.
+// biases (one value per projection row) are added first. With `norm_whole` the RMSNorm runs over the
+// whole projection row (all heads of q, or of k, together; the weight then has one value per row
+// element) instead of head by head. All arithmetic is 32-bit and the result is rounded once.
 #define TS_PDL_CLASS PDL_ELEMENTWISE
 #include "common.cuh"
 
@@ -35,6 +36,17 @@ template <> struct Pair<bf16> {
   static constexpr uintptr_t MASK = 3;
 };
 
+// 1 / sqrt(mean(x^2) + eps) over a whole projection row of n elements (bias added first), by one warp.
+template <typename T>
+__device__ __forceinline__ float whole_rstd(const T* __restrict__ x, const T* __restrict__ bias, int n, float eps, int lane) {
+  float ss = 0.f;
+  for (int i = lane; i < n; i += 32) {
+    const float v = to_float(x[i]) + (bias ? to_float(bias[i]) : 0.f);
+    ss = fmaf(v, v, ss);
+  }
+  return rsqrtf(warp_sum(ss) / (float)n + eps);
+}
+
 // One head by one warp: the head is read once from global memory into the warp's row of shared
 // memory (as 32-bit values), the sum of squares is formed on the way, and every element is then
 // written with its rotation partner taken from that row. Heads of an even size at an aligned
@@ -44,7 +56,8 @@ __device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const 
                                                  const T* __restrict__ w, float eps,
                                                  const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                  int rotary_dim, int d, T* __restrict__ dst, int lane,
-                                                 float* __restrict__ row) {
+                                                 float* __restrict__ row, const T* __restrict__ whole = nullptr,
+                                                 const T* __restrict__ whole_bias = nullptr, int whole_n = 0) {
   const bool pairs = (d & 1) == 0 &&
       ((((uintptr_t)x) | ((uintptr_t)dst) | ((uintptr_t)w) | ((uintptr_t)bias)) & Pair<T>::MASK) == 0;
   const int half = rotary_dim >> 1;
@@ -90,7 +103,7 @@ __device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const 
         ss = fmaf(a[j], a[j], fmaf(b[j], b[j], ss));
       }
     }
-    const float rstd = w ? rsqrtf(warp_sum(ss) / (float)d + eps) : 1.f;
+    const float rstd = !w ? 1.f : whole ? whole_rstd(whole, whole_bias, whole_n, eps, lane) : rsqrtf(warp_sum(ss) / (float)d + eps);
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < J; ++j) {
@@ -115,7 +128,7 @@ __device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const 
     row[i] = w ? v * to_float(w[i]) : v;
     ss = fmaf(v, v, ss);
   }
-  const float rstd = w ? rsqrtf(warp_sum(ss) / (float)d + eps) : 1.f;
+  const float rstd = !w ? 1.f : whole ? whole_rstd(whole, whole_bias, whole_n, eps, lane) : rsqrtf(warp_sum(ss) / (float)d + eps);
   __syncwarp();
   for (int i = lane; i < d; i += 32) {
     float y = row[i] * rstd;
@@ -136,7 +149,7 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, int q_stride, con
                                    const T* __restrict__ k_w, float eps, const float* __restrict__ cos_tab,
                                    const float* __restrict__ sin_tab, int rotary_dim, const int* __restrict__ slots,
                                    T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int num_tokens,
-                                   int heads, int kv_heads, int d, int dv, T* __restrict__ q_out) {
+                                   int heads, int kv_heads, int d, int dv, T* __restrict__ q_out, int norm_whole) {
   __shared__ float rows[QP_WARPS][QP_MAX_DIM];
   float* row = rows[threadIdx.x >> 5];
   pdl_trigger();
@@ -149,16 +162,25 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, int q_stride, con
   const float* cos_t = rotary_dim ? cos_tab + (size_t)t * (rotary_dim >> 1) : nullptr;
   const float* sin_t = rotary_dim ? sin_tab + (size_t)t * (rotary_dim >> 1) : nullptr;
   if (job < heads) {
-    norm_rotate_head(q_in + (size_t)t * q_stride + job * d, q_b ? q_b + job * d : nullptr, q_w, eps, cos_t, sin_t, rotary_dim, d,
-                     q_out + ((size_t)t * heads + job) * d, lane, row);
+    if (norm_whole && q_w)
+      norm_rotate_head(q_in + (size_t)t * q_stride + job * d, q_b ? q_b + job * d : nullptr, q_w + job * d, eps, cos_t, sin_t,
+                       rotary_dim, d, q_out + ((size_t)t * heads + job) * d, lane, row, q_in + (size_t)t * q_stride, q_b, heads * d);
+    else
+      norm_rotate_head(q_in + (size_t)t * q_stride + job * d, q_b ? q_b + job * d : nullptr, q_w, eps, cos_t, sin_t, rotary_dim, d,
+                       q_out + ((size_t)t * heads + job) * d, lane, row);
     return;
   }
   const int slot = slots[t];
   const int page = slot / page_size, off = slot - page * page_size;
   if (job < heads + kv_heads) {
     const int g = job - heads;
-    norm_rotate_head(k_in + (size_t)t * k_stride + g * d, k_b ? k_b + g * d : nullptr, k_w, eps, cos_t, sin_t, rotary_dim, d,
-                     k_cache + (((size_t)page * kv_heads + g) * page_size + off) * d, lane, row);
+    T* dst = k_cache + (((size_t)page * kv_heads + g) * page_size + off) * d;
+    if (norm_whole && k_w)
+      norm_rotate_head(k_in + (size_t)t * k_stride + g * d, k_b ? k_b + g * d : nullptr, k_w + g * d, eps, cos_t, sin_t,
+                       rotary_dim, d, dst, lane, row, k_in + (size_t)t * k_stride, k_b, kv_heads * d);
+    else
+      norm_rotate_head(k_in + (size_t)t * k_stride + g * d, k_b ? k_b + g * d : nullptr, k_w, eps, cos_t, sin_t, rotary_dim, d,
+                       dst, lane, row);
     return;
   }
   const int g = job - heads - kv_heads;
@@ -192,7 +214,7 @@ extern "C" int ts_qkv_prepare(const void* q_in, int q_stride, const void* k_in, 
                               int v_stride, const void* q_b, const void* k_b, const void* v_b, const void* q_w, const void* k_w, float eps, const float* cos_tab,
                               const float* sin_tab, int rotary_dim, const int* slots, void* k_cache, void* v_cache,
                               int page_size, int num_tokens, int heads, int kv_heads, int d, int dv, void* q_out,
-                              int dtype, cudaStream_t stream) {
+                              int norm_whole, int dtype, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (d > QP_MAX_DIM) return TS_ERR_UNSUPPORTED;
   if (rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || (rotary_dim && (!cos_tab || !sin_tab))) return TS_ERR_BAD_ARGUMENT;
@@ -204,11 +226,11 @@ extern "C" int ts_qkv_prepare(const void* q_in, int q_stride, const void* k_in, 
     return launch(qkv_prepare_kernel<float>, blocks, threads, 0, stream, (const float*)q_in, q_stride, (const float*)k_in,
                   k_stride, (const float*)v_in, v_stride, (const float*)q_b, (const float*)k_b, (const float*)v_b, (const float*)q_w, (const float*)k_w, eps, cos_tab, sin_tab,
                   rotary_dim, slots, (float*)k_cache, (float*)v_cache, page_size, num_tokens, heads, kv_heads, d, dv,
-                  (float*)q_out);
+                  (float*)q_out, norm_whole);
   if (dtype == TS_DTYPE_BF16)
     return launch(qkv_prepare_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)q_in, q_stride, (const bf16*)k_in,
                   k_stride, (const bf16*)v_in, v_stride, (const bf16*)q_b, (const bf16*)k_b, (const bf16*)v_b, (const bf16*)q_w, (const bf16*)k_w, eps, cos_tab, sin_tab,
                   rotary_dim, slots, (bf16*)k_cache, (bf16*)v_cache, page_size, num_tokens, heads, kv_heads, d, dv,
-                  (bf16*)q_out);
+                  (bf16*)q_out, norm_whole);
   return TS_ERR_BAD_ARGUMENT;
 }

@@ -12,6 +12,7 @@ from __future__ import annotations
 import ctypes
 import math
 import os
+from dataclasses import dataclass
 from typing import Any, Callable, Sequence
 
 import torch
@@ -44,16 +45,17 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_add_bias": [_vp, _vp, _i, _i, _i, _vp],
     "ts_tanh": [_vp, _c.c_size_t, _i, _vp],
     "ts_linear_scan": [_i, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _i, _vp, _vp,
-                       _vp],
+                       _f, _f, _vp],
     "ts_token_shift_mix": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _vp, _i, _vp],
     "ts_softcap": [_vp, _c.c_size_t, _f, _vp],
+    "ts_rms_norm_rows": [_vp, _c.c_longlong, _vp, _f, _vp, _i, _i, _i, _vp],
     "ts_head_norm_gate": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
     "ts_post_norm_add_rms_norm": [_vp, _vp, _vp, _vp, _f, _i, _f, _vp, _i, _f, _vp, _vp, _i, _i, _i, _vp],
     "ts_mlstm_scan": [_vp, _i, _i, _i, _i, _vp, _vp, _f, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp],
     "ts_delta_scan": [_vp, _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ts_causal_conv_silu": [_vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp],
     "ts_qkv_prepare": [_vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i,
-                       _i, _i, _vp, _i, _vp],
+                       _i, _i, _vp, _i, _i, _vp],
     "ts_prefill_attention_mma": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "ts_decode_attention_mma": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp,
                                 _vp, _vp],
@@ -83,14 +85,14 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_gemm_skinny_gated": [_vp, _vp, _vp, _i, _i, _i, _i, _f, _vp],
     "ts_latent_prepare": [_vp, _c.c_longlong, _vp, _vp, _c.c_longlong, _vp, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i,
                           _i, _i, _i, _vp],
-    "ts_latent_attention": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _i, _vp],
+    "ts_latent_attention": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp],
     "ts_latent_attention_mma_takes": [_i, _i],
-    "ts_moe_route": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp],
+    "ts_moe_route": [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp],
     "ts_moe_route_fused": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp],
     "ts_moe_gather": [_vp, _vp, _vp, _i, _i, _vp],
     "ts_moe_gemm_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp],
     "ts_moe_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
-    "ts_moe_combine": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ts_moe_combine": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp],
     "ts_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 _fns: dict[str, Any] = {}
@@ -1199,6 +1201,17 @@ def head_norm_gate(x: torch.Tensor, weight: torch.Tensor | None, weight_per_head
         float(eps), int(bool(gate_per_head)), int(bool(gate_silu)), _code(dt), _stream()), "head_norm_gate")
 
 
+def rms_norm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """``out[r] = dt(x[r] / sqrt(mean(x[r]^2) + eps) * weight)`` in 32-bit, rounded once; ``x [R, w]`` dt with unit
+    column stride (a column slice of a wider product is fine), ``weight [w]`` dt, ``out [R, w]`` dt contiguous."""
+    r, w = out.shape
+    dt = out.dtype
+    if tuple(x.shape) != (r, w) or x.dtype != dt or x.stride(1) != 1 or not x.is_cuda or weight.shape != (w,):
+        raise KernelError("rms_norm_rows: shapes, dtypes or the column stride")
+    _check(_fn("ts_rms_norm_rows")(x.data_ptr(), x.stride(0), _dev(weight, "weight", dt), float(eps), _dev(out, "out"), r, w,
+                                   _code(dt), _stream()), "rms_norm_rows")
+
+
 # ---------------------------------------------------------------- recurrent mixers
 SCAN_MAX_KEY_DIM = 256
 SCAN_MAX_TAPS = 8
@@ -1302,18 +1315,30 @@ def linear_scan_decay(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: 
     _linear_scan(1, q, k, v, None, None, None, decay, state, ctx, heads, d, dv, out)
 
 
+def linear_scan_gated(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w_pre: torch.Tensor, w_bias: torch.Tensor,
+                      tau: float, q_scale: float, state: torch.Tensor, ctx: Any, heads: int, d: int, dv: int,
+                      out: torch.Tensor) -> None:
+    """Gated linear attention with a decay per key channel and token, ``alpha = sigmoid(w_pre + w_bias)^(1/tau)``
+    (formed in 32-bit as ``exp(logsigmoid(.) / tau)``): per head ``S <- diag(alpha) S + k v^T``, ``o = S^T (q_scale q)``
+    (the read-out sees the current token's write). Shapes as for ``linear_scan_bonus``."""
+    if not tau > 0:
+        raise KernelError("linear_scan_gated: tau must be positive")
+    _linear_scan(2, q, k, v, w_pre, w_bias, None, None, state, ctx, heads, d, dv, out, inv_tau=1.0 / tau, q_scale=q_scale)
+
+
 def _linear_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w_pre: torch.Tensor | None,
                  w_bias: torch.Tensor | None, bonus: torch.Tensor | None, decay: torch.Tensor | None,
-                 state: torch.Tensor, ctx: Any, heads: int, d: int, dv: int, out: torch.Tensor) -> None:
+                 state: torch.Tensor, ctx: Any, heads: int, d: int, dv: int, out: torch.Tensor,
+                 inv_tau: float = 0.0, q_scale: float = 1.0) -> None:
     t, dt = q.shape[0], q.dtype
     for name, x, width in (("q", q, heads * d), ("k", k, heads * d), ("v", v, heads * dv)):
         if not x.is_cuda or x.dtype != dt or x.shape != (t, width) or x.stride(1) != 1:
             raise KernelError(f"linear_scan: {name} must be [T, {width}] {dt} with unit column stride on the device")
     if tuple(out.shape) != (t, heads, dv) or d > SCAN_MAX_KEY_DIM:
         raise KernelError("linear_scan: out shape or key size")
-    if mode == 0:
+    if mode in (0, 2):
         if (w_pre.shape != (t, heads * d) or w_pre.dtype != torch.float32 or w_pre.stride(1) != 1
-                or w_bias.shape != (heads * d,) or bonus.shape != (heads * d,)):
+                or w_bias.shape != (heads * d,) or (mode == 0 and bonus.shape != (heads * d,))):
             raise KernelError("linear_scan: decay pre-activations, their bias or the bonus")
     elif decay.shape != (heads,):
         raise KernelError("linear_scan: one decay per head")
@@ -1322,7 +1347,7 @@ def _linear_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w
     seg_state = seg_decay = None
     if max_segs > 1:
         seg_state = ctx.arena.take((ctx.num_seqs * max_segs, heads * d * dv), torch.float32)
-        if mode == 0:
+        if mode in (0, 2):
             seg_decay = ctx.arena.take((ctx.num_seqs * max_segs, heads * d), torch.float32)
     _check(_fn("ts_linear_scan")(
         mode, q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
@@ -1331,8 +1356,9 @@ def _linear_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w
         state_ptr, state_stride, _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
         _dev(ctx.state_slots, "state_slots", torch.int32), ctx.num_seqs, heads, d, dv,
         _dev(out, "out", torch.float32), _code(dt), int(ctx.max_query_len), seg_len, max_segs,
-        None if seg_state is None else seg_state.data_ptr(), None if seg_decay is None else seg_decay.data_ptr(), _stream()),
-        "linear_scan", kernels=1 if max_segs <= 1 else (4 if mode == 0 else 3))
+        None if seg_state is None else seg_state.data_ptr(), None if seg_decay is None else seg_decay.data_ptr(),
+        float(inv_tau), float(q_scale), _stream()),
+        "linear_scan", kernels=1 if max_segs <= 1 else (4 if mode in (0, 2) else 3))
 
 
 # A portion of this many tokens or more is cut into segments that run side by side.
@@ -1457,8 +1483,9 @@ def qkv_prepare(q_in: torch.Tensor, k_in: torch.Tensor | None, v_in: torch.Tenso
                 rotary_dim: int, slots: torch.Tensor | None, k_cache: torch.Tensor | None, v_cache: torch.Tensor | None,
                 page_size: int, heads: int, kv_heads: int, d: int, dv: int, q_out: torch.Tensor,
                 q_bias: torch.Tensor | None = None, k_bias: torch.Tensor | None = None,
-                v_bias: torch.Tensor | None = None) -> None:
-    """Per (token, head): optional bias (one value per projection row, dt), optional RMSNorm over the head with a plain weight, rotation of the first
+                v_bias: torch.Tensor | None = None, norm_whole: bool = False) -> None:
+    """Per (token, head): optional bias (one value per projection row, dt), optional RMSNorm over the head with a plain weight
+    (``norm_whole``: over all heads of q, or of k, together, with weights of ``heads * d`` and ``kv_heads * d`` values), rotation of the first
     ``rotary_dim`` elements (i pairs with i + rotary_dim / 2); queries to ``q_out [T, heads, d]``,
     keys and (unchanged) values to the caches at the tokens' slots (when ``k_in`` is given).
     ``q_in``/``k_in``/``v_in`` are 2-D dt with unit column stride (column slices of a merged
@@ -1476,6 +1503,9 @@ def qkv_prepare(q_in: torch.Tensor, k_in: torch.Tensor | None, v_in: torch.Tenso
         _check_indices("qkv_prepare", None, None, page_size, k_cache.shape[0], slots)
     if rotary_dim and (cos is None or tuple(cos.shape) != (t, rotary_dim // 2) or tuple(sin.shape) != tuple(cos.shape)):
         raise KernelError("qkv_prepare: rotary tables missing or of the wrong shape")
+    for name, w, width in (("q_weight", q_weight, heads * d), ("k_weight", k_weight, kv_heads * d)):
+        if w is not None and w.numel() != (width if norm_whole else d):
+            raise KernelError(f"qkv_prepare: {name} must have {width if norm_whole else d} values")
     _check(_fn("ts_qkv_prepare")(
         q_in.data_ptr(), q_in.stride(0), None if k_in is None else k_in.data_ptr(), 0 if k_in is None else k_in.stride(0),
         None if v_in is None else v_in.data_ptr(), 0 if v_in is None else v_in.stride(0),
@@ -1484,7 +1514,7 @@ def qkv_prepare(q_in: torch.Tensor, k_in: torch.Tensor | None, v_in: torch.Tenso
         _opt(q_weight, "q_weight", dt), _opt(k_weight, "k_weight", dt), float(eps),
         _opt(cos, "cos", torch.float32), _opt(sin, "sin", torch.float32), int(rotary_dim),
         _opt(slots, "slots", torch.int32), _opt(k_cache, "k_cache", dt), _opt(v_cache, "v_cache", dt), page_size, t,
-        heads, kv_heads, d, dv, _dev(q_out, "q_out"), _code(dt), _stream()), "qkv_prepare")
+        heads, kv_heads, d, dv, _dev(q_out, "q_out"), int(bool(norm_whole)), _code(dt), _stream()), "qkv_prepare")
 
 
 # ------------------------------------------------------------- latent attention
@@ -1534,11 +1564,12 @@ def latent_prepare(q_in: torch.Tensor, q_folded: torch.Tensor, ckr: torch.Tensor
 
 
 def latent_attention(q: torch.Tensor, cache: torch.Tensor, page_size: int, block_tables: torch.Tensor, ctx: Any,
-                     rank: int, scale: float, window: int, out: torch.Tensor) -> None:
+                     rank: int, scale: float, window: int, out: torch.Tensor, sinks: torch.Tensor | None = None) -> None:
     """Causal attention of the query rows ``q [T, H, rank + rot]`` over each request's cached rows
     (``cache [pages * page_size, rank + rot]``: one row per position, shared by all heads); the
     values are the first ``rank`` elements of the keys. ``window`` 0 means all earlier positions.
-    ``out [T, H, rank]`` dt."""
+    ``sinks`` (float32 ``[H]``, optional): a logit per head that joins the softmax's denominator, unscaled,
+    without a value. ``out [T, H, rank]`` dt."""
     t, heads, d = q.shape
     dt = q.dtype
     if cache.dtype != dt or out.dtype != dt or cache.dim() != 2 or cache.shape[1] != d or tuple(out.shape) != (t, heads, rank):
@@ -1547,6 +1578,8 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, page_size: int, block
         raise KernelError(f"latent_attention: latent size {rank} must be at most {LATENT_MAX_RANK}")
     if block_tables.dim() != 2 or block_tables.shape[0] != ctx.num_seqs:
         raise KernelError("latent_attention: block_tables must be [requests, width]")
+    if sinks is not None and (sinks.shape != (heads,) or sinks.dtype != torch.float32):
+        raise KernelError("latent_attention: sinks must be float32, one per head")
     _check_indices("latent_attention", block_tables, ctx, page_size, cache.shape[0] // page_size)
     mma = bool(LATENT_TENSOR_CORES and dt == torch.bfloat16 and _fn("ts_latent_attention_mma_takes")(rank, d - rank))
     splits, part_acc, part_ml = 1, None, None
@@ -1561,7 +1594,8 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, page_size: int, block
         block_tables.shape[1], _dev(ctx.cu_query_lens, "cu_query_lens", torch.int32),
         _dev(ctx.context_lens_dev, "context_lens", torch.int32), ctx.num_seqs, ctx.max_query_len, heads, rank, d - rank,
         page_size, float(scale), int(window), _code(dt), int(mma), splits, _opt(part_acc, "part_acc"),
-        _opt(part_ml, "part_ml"), t, _stream()), "latent_attention", kernels=2 if splits > 1 else 1)
+        _opt(part_ml, "part_ml"), t, _opt(sinks, "sinks", torch.float32), _stream()), "latent_attention",
+        kernels=2 if splits > 1 else 1)
 
 
 def bmm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -1636,45 +1670,85 @@ def _moe_plan(t: int, e: int, top: int, arena: Any, tile_rows: int) -> dict[str,
     return plan
 
 
+@dataclass(frozen=True)
+class RouteRule:
+    """How a token's experts and their weights follow from its router outputs. ``scored=False``: the ``top``
+    largest logits, weighted by the softmax over the picked logits alone. ``scored=True``: scores are the
+    softmax over ALL outputs; the choice looks at ``score + correction`` (``correction`` float32, one per output,
+    or None) and only inside the ``keep`` best of ``groups`` equal groups of neighbouring outputs (a group's
+    value is its largest choice score; the others' count as minus infinity); the weights are the picks' scores
+    over their sum (+ 1e-20), times ``scale``. ``identity``: the last outputs are experts without matrices
+    whose output is their input; their picks take no row of the sorted order."""
+
+    scored: bool = False
+    groups: int = 1
+    keep: int = 1
+    scale: float = 1.0
+    identity: int = 0
+    correction: torch.Tensor | None = None
+
+
+PLAIN_ROUTE = RouteRule()
+
+
 def moe_route_from(x: torch.Tensor, w_router: torch.Tensor, top: int, counts: torch.Tensor, arena: Any,
-                   tile_rows: int = MOE_TILE_ROWS) -> dict[str, Any]:
-    """Router logits ``x W_router^T`` (32-bit sums and output) and :func:`moe_route` on them. A step of few
+                   tile_rows: int = MOE_TILE_ROWS, rule: RouteRule = PLAIN_ROUTE, outputs: int | None = None) -> dict[str, Any]:
+    """Router logits ``x W_router^T`` (32-bit sums and output) and :func:`moe_route` on them. ``outputs``: how
+    many of the first rows of ``w_router`` are router outputs (all by default); rows beyond ride along in the
+    same product (a gate of a shared expert) and are found in ``plan["logits"]``. A step of few
     tokens can do both in the one CTA that routes (no launch for the router's product); its sums run in
     another order than the product's, so a token's logits differ in the last bits between the two;
-    switched by ``MOE_ROUTE_FUSED_MAX_WORK``, off by default)."""
+    switched by ``MOE_ROUTE_FUSED_MAX_WORK``, off by default, plain rule only)."""
     t, k = x.shape
     e = w_router.shape[0]
     if w_router.shape[1] != k or x.dtype != w_router.dtype:
         raise KernelError("moe_route_from: shapes or dtypes")
     logits = arena.take((t, e), torch.float32)
-    if t <= 64 and e <= 1024 and t * e * k <= MOE_ROUTE_FUSED_MAX_WORK and 0 < top <= min(e, 32):
+    if (rule is PLAIN_ROUTE and outputs in (None, e) and t <= 64 and e <= 1024 and t * e * k <= MOE_ROUTE_FUSED_MAX_WORK
+            and 0 < top <= min(e, 32)):
         plan = _moe_plan(t, e, top, arena, tile_rows)
         _check(_fn("ts_moe_route_fused")(
             _dev(x, "x"), _dev(w_router, "w_router"), k, _code(x.dtype), _dev(logits, "logits", torch.float32), t, e, top,
             plan["ids"].data_ptr(), plan["weights"].data_ptr(), plan["place"].data_ptr(), plan["offsets"].data_ptr(),
             plan["tile_expert"].data_ptr(), plan["tile_row0"].data_ptr(), plan["num_tiles"].data_ptr(), plan["max_tiles"],
             plan["row_of"].data_ptr(), plan["token_of"].data_ptr(), tile_rows, _stream()), "moe_route_fused")
+        plan["logits"] = logits
         return plan
     gemm(x, w_router, logits)
-    return moe_route(logits, top, counts, arena, tile_rows)
+    return moe_route(logits, top, counts, arena, tile_rows, rule, outputs)
 
 
-def moe_route(logits: torch.Tensor, top: int, counts: torch.Tensor, arena: Any, tile_rows: int = MOE_TILE_ROWS) -> dict[str, Any]:
-    """From router logits ``[T, E]`` float32: every token's ``top`` experts (largest logits, ties to
-    the lower index), their weights (softmax over the picked logits only), and the sorted order in
-    which the products run: rows grouped by expert, cut into tiles. ``counts`` is ``[E]`` int32,
-    zero before the call and zero again after it. Returns the plan's device arrays."""
-    t, e = logits.shape
-    if not 0 < top <= min(e, 32) or counts.shape != (e,):
-        raise KernelError("moe_route: top must be between 1 and min(experts, 32); counts one per expert")
-    tiles = moe_max_tiles(t, top, e, tile_rows)
-    plan = _moe_plan(t, e, top, arena, tile_rows)
+def moe_route(logits: torch.Tensor, top: int, counts: torch.Tensor, arena: Any, tile_rows: int = MOE_TILE_ROWS,
+              rule: RouteRule = PLAIN_ROUTE, outputs: int | None = None) -> dict[str, Any]:
+    """From router logits ``[T, >= outputs]`` float32 (the first ``outputs`` columns; all by default): every
+    token's ``top`` experts and their weights by ``rule`` (ties to the lower index), and the sorted order in
+    which the products run: rows grouped by expert, cut into tiles. ``counts`` is int32, one per expert with
+    matrices (``outputs - rule.identity``), zero before the call and zero again after it. Returns the plan's
+    device arrays; ``plan["experts"]`` counts the experts with matrices."""
+    t, ld = logits.shape
+    e = ld if outputs is None else int(outputs)
+    real = e - rule.identity
+    if not 0 < e <= ld or real <= 0 or logits.stride(1) != 1:
+        raise KernelError("moe_route: outputs, identity experts or the logits' layout")
+    if not 0 < top <= min(e, 32) or counts.shape != (real,):
+        raise KernelError("moe_route: top must be between 1 and min(outputs, 32); counts one per expert with matrices")
+    if not rule.scored and (rule.identity or rule.groups > 1 or rule.correction is not None):
+        raise KernelError("moe_route: groups, a correction and identity experts come with the scored rule")
+    if rule.groups < 1 or rule.groups > 32 or e % rule.groups or not 1 <= rule.keep <= rule.groups or e // rule.groups * rule.keep < top:
+        raise KernelError("moe_route: up to 32 equal groups, of which the kept ones must hold at least `top` outputs")
+    if rule.correction is not None and (rule.correction.shape != (e,) or rule.correction.dtype != torch.float32):
+        raise KernelError("moe_route: the correction must be float32, one value per output")
+    tiles = moe_max_tiles(t, top, real, tile_rows)
+    plan = _moe_plan(t, real, top, arena, tile_rows)
     _check(_fn("ts_moe_route")(
-        _dev(logits, "logits", torch.float32), t, e, top, plan["ids"].data_ptr(), plan["weights"].data_ptr(),
-        plan["place"].data_ptr(), _dev(counts, "counts", torch.int32), plan["offsets"].data_ptr(),
+        _dev(logits, "logits", torch.float32), logits.stride(0), t, e, real, top, int(rule.scored), rule.groups, rule.keep,
+        float(rule.scale), _opt(rule.correction, "correction", torch.float32), plan["ids"].data_ptr(),
+        plan["weights"].data_ptr(), plan["place"].data_ptr(), _dev(counts, "counts", torch.int32), plan["offsets"].data_ptr(),
         plan["tile_expert"].data_ptr(), plan["tile_row0"].data_ptr(), plan["num_tiles"].data_ptr(), tiles,
         plan["row_of"].data_ptr(), plan["token_of"].data_ptr(), tile_rows, _stream()), "moe_route",
         kernels=1 if t <= 64 else 3)
+    plan["logits"] = logits
+    plan["identity"] = rule.identity
     return plan
 
 
@@ -1711,16 +1785,28 @@ def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: dict[str
         _stream()), "moe_gemm")
 
 
-def moe_combine(y: torch.Tensor, plan: dict[str, Any], shared_out: torch.Tensor | None, out: torch.Tensor) -> None:
-    """``out[t] = dt(sum_j weight[t, j] * y[row_of[t, j]] (+ shared_out[t]))`` in 32-bit."""
+def moe_combine(y: torch.Tensor, plan: dict[str, Any], shared_out: torch.Tensor | None, out: torch.Tensor,
+                x: torch.Tensor | None = None, shared_gate: torch.Tensor | None = None) -> None:
+    """``out[t] = dt(sum_j weight[t, j] * y[row_of[t, j]] (+ g[t] * shared_out[t]))`` in 32-bit. A pick of an
+    identity expert contributes ``weight * x[t]`` (``x [T, hidden]`` dt: the experts' input; needed when the plan
+    has identity experts). ``shared_gate`` (float32 ``[T]``, possibly a column of a wider matrix): ``g =
+    sigmoid(shared_gate)``; without it ``g = 1``."""
     t, h = out.shape
     if tuple(y.shape) != (plan["picks"], h) or t * plan["top"] != plan["picks"] or y.dtype != out.dtype:
         raise KernelError("moe_combine: shapes or dtypes")
     if shared_out is not None and (tuple(shared_out.shape) != (t, h) or shared_out.dtype != out.dtype):
         raise KernelError("moe_combine: the shared output must be [T, hidden] dt")
+    if plan.get("identity", 0) and x is None:
+        raise KernelError("moe_combine: identity experts need the experts' input")
+    if x is not None and (tuple(x.shape) != (t, h) or x.dtype != out.dtype or not x.is_contiguous()):
+        raise KernelError("moe_combine: x must be [T, hidden] dt")
+    if shared_gate is not None and (shared_out is None or shared_gate.shape != (t,) or shared_gate.dtype != torch.float32):
+        raise KernelError("moe_combine: the shared gate is one float32 logit per token and needs a shared output")
     _check(_fn("ts_moe_combine")(_dev(y, "y"), plan["row_of"].data_ptr(), plan["weights"].data_ptr(),
-                                 _opt(shared_out, "shared_out"), _dev(out, "out"), t, plan["top"], h, _code(out.dtype),
-                                 _stream()), "moe_combine")
+                                 _opt(shared_out, "shared_out"), _dev(out, "out"), t, plan["top"], h, _opt(x, "x"),
+                                 None if shared_gate is None else shared_gate.data_ptr(),
+                                 0 if shared_gate is None else shared_gate.stride(0), _code(out.dtype), _stream()),
+           "moe_combine")
 
 
 # --------------------------------------------------------------------- sampling

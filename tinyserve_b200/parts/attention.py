@@ -139,7 +139,10 @@ class GatedSinkAttention(Mixer):
     makes ``W_g`` ``[num_heads, hidden]``, one gate value for a whole head; ``window`` limits every
     query to the last ``window`` positions, itself included, and ``keep_first`` (with a window) leaves
     the first ``keep_first`` positions visible to every later query all the same; ``qkv_bias`` adds a
-    bias to q, k and v (the projection's name with ``.b`` added) before the norms. With
+    bias to q, k and v (the projection's name with ``.b`` added) before the norms. ``qk_norm="all"``
+    norms q (and k) over the whole projection, all heads together, with weights of that size, instead of
+    head by head. ``values="keys"``: there is no ``W_v``; the values are the keys as projected, before norm
+    and rotation (``value_dim`` must equal ``key_dim``). With
     ``own_kv=False`` the layer has no key/value tensors and only ever runs as a call that reads
     another call's cache. ``names`` maps the roles "q", "k", "v", "gate", "out", "q_norm",
     "k_norm", "sink" to tensor names after the prefix.
@@ -154,7 +157,14 @@ class GatedSinkAttention(Mixer):
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
                  scale: float, qk_norm: bool = True, qk_norm_eps: float = 1e-6, sink: "bool | str" = True,
                  own_kv: bool = True, names: Mapping[str, str] | None = None, window: int | None = None,
-                 gate: str = "element", keep_first: int = 0, qkv_bias: bool = False) -> None:
+                 gate: str = "element", keep_first: int = 0, qkv_bias: bool = False, values: str = "own") -> None:
+        if qk_norm not in (True, False, "head", "all"):
+            raise ValueError(f"qk_norm={qk_norm!r}: True / 'head' (per head), 'all' (over the whole projection) or False")
+        if values not in ("own", "keys") or (values == "keys" and value_dim != key_dim):
+            raise ValueError(f"values={values!r}: 'own' (a projection of their own) or 'keys' (then value_dim must equal key_dim)")
+        self.norm_whole, self.values_are_keys = qk_norm == "all", values == "keys"
+        if self.values_are_keys and qkv_bias:
+            raise NotImplementedError("biases on q, k, v together with values that are the keys")
         if keep_first < 0 or (keep_first and window is None):
             raise ValueError(f"keep_first={keep_first} must not be negative and needs a window")
         self.keep_first, self.qkv_bias = int(keep_first), bool(qkv_bias)
@@ -186,13 +196,16 @@ class GatedSinkAttention(Mixer):
 
     def _widths(self) -> tuple[int, int, int, int]:
         """Rows of the q, k, v and gate products."""
-        return (self.heads * self.d, self.groups * self.d, self.groups * self.dv,
+        return (self.heads * self.d, self.groups * self.d, 0 if self.values_are_keys else self.groups * self.dv,
                 self.heads if self.gate_per_head else self.heads * self.dv)
 
     def tensor_specs(self, prefix: str) -> list[TensorSpec]:
         p, n, h = prefix + self.prefix, self.names, self.h
         q, k, v, g = self._widths()
-        if self.own_kv:
+        if self.own_kv and self.values_are_keys:
+            specs = [TensorSpec(p + "qkg", (q + k + g, h), merged_from=tuple(p + n[r] for r in ("q", "k", "gate")),
+                                merged_rows=(q, k, g))]
+        elif self.own_kv:
             specs = [TensorSpec(p + "qkvg", (q + k + v + g, h), merged_from=tuple(p + n[r] for r in ("q", "k", "v", "gate")),
                                 merged_rows=(q, k, v, g))]
         else:
@@ -205,16 +218,16 @@ class GatedSinkAttention(Mixer):
             else:
                 specs.append(TensorSpec(p + n["q"] + ".b", (q,)))
         if self.qk_norm:
-            specs.append(TensorSpec(p + n["q_norm"], (self.d,), init="one_plus_normal"))
+            specs.append(TensorSpec(p + n["q_norm"], (q if self.norm_whole else self.d,), init="one_plus_normal"))
             if self.own_kv:
-                specs.append(TensorSpec(p + n["k_norm"], (self.d,), init="one_plus_normal"))
+                specs.append(TensorSpec(p + n["k_norm"], (k if self.norm_whole else self.d,), init="one_plus_normal"))
         if self.learned_sink:
             specs.append(TensorSpec(p + n["sink"], (self.heads,), std=1.0))
         return specs
 
     def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
         p, n = prefix + self.prefix, self.names
-        self.w_in = tensors[p + ("qkvg" if self.own_kv else "qg")]
+        self.w_in = tensors[p + (("qkg" if self.values_are_keys else "qkvg") if self.own_kv else "qg")]
         self.w_o = tensors[p + n["out"]]
         if self.qkv_bias:
             self.b_in = tensors[p + ("qkv.b" if self.own_kv else n["q"] + ".b")]
@@ -238,15 +251,17 @@ class GatedSinkAttention(Mixer):
         if rot is not None and rot.interleaved:
             raise NotImplementedError("this mixer rotates pairs (i, i + rotary_dim / 2) only")
         queries = arena.take((t, self.heads, self.d), ctx.dtype)
+        values = proj[:, q: q + k] if self.values_are_keys else proj[:, q + k: q + k + v]
         ops.qkv_prepare(proj[:, :q], proj[:, q: q + k] if writes_cache else None,
-                        proj[:, q + k: q + k + v] if writes_cache else None, self.q_norm_w, self.k_norm_w, self.eps,
+                        values if writes_cache else None, self.q_norm_w, self.k_norm_w, self.eps,
                         None if rot is None else rot.cos, None if rot is None else rot.sin,
                         0 if rot is None else rot.rotary_dim, group.slots if writes_cache else None,
                         cache.k if writes_cache else None, cache.v if writes_cache else None, cache.page_size,
                         self.heads, self.groups, self.d, self.dv, queries,
                         q_bias=None if self.b_in is None else self.b_in[:q],
                         k_bias=None if self.b_in is None or not writes_cache else self.b_in[q: q + k],
-                        v_bias=None if self.b_in is None or not writes_cache else self.b_in[q + k: q + k + v])
+                        v_bias=None if self.b_in is None or not writes_cache else self.b_in[q + k: q + k + v],
+                        norm_whole=self.norm_whole)
         width = self.heads * self.dv
         attn = arena.take((t, width), ctx.dtype)
         ops.paged_attention(queries, cache.k, cache.v, cache.page_size, group.block_tables, ctx, self.scale,
@@ -273,15 +288,24 @@ class LatentAttention(Mixer):
     up-projection is folded into the queries (``q'_a = W_uk,a^T q_nope,a``, a product per head) so
     that every head scores against the cached row itself, and the values' up-projection is applied
     to the weighted sum of latents (another product per head): attention with one shared key/value
-    head whose values are the first ``rank`` elements of its keys. ``names`` maps the roles "q",
-    "down", "down_norm", "up_k", "up_v", "out" to tensor names after the prefix."""
+    head whose values are the first ``rank`` elements of its keys.
+
+    ``q_rank``: the queries go through a latent of their own, ``q = W_uq RMSnorm(W_dq h)`` (plain weight, the
+    same eps), instead of ``W_q h``. ``sink``: a learned logit per head joins the softmax's denominator
+    (unscaled, without a value). ``names`` maps the roles "q", "down", "down_norm", "up_k", "up_v", "out",
+    "q_down", "q_down_norm", "q_up", "sink" to tensor names after the prefix."""
 
     recordable = EVERY_STEP
-    _NAMES = {"q": "q", "down": "dkv", "down_norm": "dkv.norm", "up_k": "uk", "up_v": "uv", "out": "o"}
+    _NAMES = {"q": "q", "down": "dkv", "down_norm": "dkv.norm", "up_k": "uk", "up_v": "uv", "out": "o",
+              "q_down": "dq", "q_down_norm": "dq.norm", "q_up": "uq", "sink": "sink"}
 
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, nope_dim: int, rope_dim: int, value_dim: int,
                  rank: int, scale: float, norm_eps: float, window: int | None = None,
-                 names: Mapping[str, str] | None = None) -> None:
+                 names: Mapping[str, str] | None = None, q_rank: int | None = None, sink: bool = False) -> None:
+        if q_rank is not None and q_rank <= 0:
+            raise ValueError(f"q_rank={q_rank} must be positive or None")
+        self.q_rank, self.has_sink = None if q_rank is None else int(q_rank), bool(sink)
+        self.sink = None
         if min(num_heads, nope_dim, value_dim, rank) <= 0 or rope_dim < 0:
             raise ValueError("latent attention: heads, head sizes and the latent size must be positive")
         if rank > ops.LATENT_MAX_RANK:
@@ -300,7 +324,16 @@ class LatentAttention(Mixer):
     def tensor_specs(self, prefix: str) -> list[TensorSpec]:
         p, n, h = prefix + self.prefix, self.names, self.h
         q, down = self.heads * (self.dn + self.dr), self.rank + self.dr
-        return [TensorSpec(p + "q+down", (q + down, h), merged_from=(p + n["q"], p + n["down"]), merged_rows=(q, down)),
+        if self.q_rank is None:
+            first = [TensorSpec(p + "q+down", (q + down, h), merged_from=(p + n["q"], p + n["down"]), merged_rows=(q, down))]
+        else:
+            first = [TensorSpec(p + n["q_down"] + "+" + n["down"], (self.q_rank + down, h), merged_from=(p + n["q_down"], p + n["down"]),
+                                merged_rows=(self.q_rank, down)),
+                     TensorSpec(p + n["q_down_norm"], (self.q_rank,), init="one_plus_normal"),
+                     TensorSpec(p + n["q_up"], (q, self.q_rank))]
+        if self.has_sink:
+            first.append(TensorSpec(p + n["sink"], (self.heads,), std=1.0))
+        return first + [
                 TensorSpec(p + n["down_norm"], (self.rank,), init="one_plus_normal"),
                 TensorSpec(p + n["up_k"], (self.heads * self.dn, self.rank)),
                 TensorSpec(p + n["up_v"], (self.heads * self.dv, self.rank)),
@@ -308,7 +341,13 @@ class LatentAttention(Mixer):
 
     def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
         p, n = prefix + self.prefix, self.names
-        self.w_in = tensors[p + "q+down"]
+        if self.q_rank is None:
+            self.w_in = tensors[p + "q+down"]
+        else:
+            self.w_in = tensors[p + n["q_down"] + "+" + n["down"]]
+            self.q_norm_w, self.w_uq = tensors[p + n["q_down_norm"]], tensors[p + n["q_up"]]
+        if self.has_sink:
+            self.sink = tensors[p + n["sink"]].float().contiguous()
         self.norm_w = tensors[p + n["down_norm"]]
         self.w_uk = tensors[p + n["up_k"]].view(self.heads, self.dn, self.rank)                    # [H, nope, rank]
         self.w_uv_t = tensors[p + n["up_v"]].view(self.heads, self.dv, self.rank).transpose(1, 2)  # [H, rank, dv] (a view)
@@ -322,20 +361,28 @@ class LatentAttention(Mixer):
         qw = hd * (self.dn + self.dr)
         proj = arena.take((t, self.w_in.shape[0]), ctx.dtype)
         ops.gemm(x, self.w_in, proj)
+        if self.q_rank is None:
+            q_rows, ckr = proj[:, :qw], proj[:, qw:]
+        else:
+            # the queries' latent: normed in 32-bit (rounded once), then up-projected
+            cq = arena.take((t, self.q_rank), ctx.dtype)
+            ops.rms_norm_rows(proj[:, : self.q_rank], self.q_norm_w, self.eps, cq)
+            q_rows, ckr = arena.take((t, qw), ctx.dtype), proj[:, self.q_rank:]
+            ops.gemm(cq, self.w_uq, q_rows)
         # the keys' up-projection folded into the queries, head by head: [H, T, nope] x [H, nope, rank]
-        q_nope = proj[:, :qw].view(t, hd, self.dn + self.dr)[:, :, : self.dn].transpose(0, 1)
+        q_nope = q_rows.view(t, hd, self.dn + self.dr)[:, :, : self.dn].transpose(0, 1)
         folded = arena.take((hd, t, self.rank), ctx.dtype)
         ops.bmm(q_nope, self.w_uk, folded)
         rot = None if position is None else position.qk_rotation()
         queries = arena.take((t, hd, self.rank + self.dr), ctx.dtype)
         rows = cache.k.view(-1, self.rank + self.dr)
-        ops.latent_prepare(proj[:, :qw], folded, proj[:, qw:], self.norm_w, self.eps,
+        ops.latent_prepare(q_rows, folded, ckr, self.norm_w, self.eps,
                            None if rot is None else rot.cos, None if rot is None else rot.sin,
                            0 if rot is None else rot.rotary_dim, False if rot is None else rot.interleaved,
                            group.slots, rows, hd, self.dn, self.rank, self.dr, queries)
         mixed = arena.take((t, hd, self.rank), ctx.dtype)
         ops.latent_attention(queries, rows, cache.page_size, group.block_tables, ctx, self.rank, self.scale,
-                             self.window or 0, mixed)
+                             self.window or 0, mixed, sinks=self.sink)
         # the values' up-projection, head by head: [H, T, rank] x [H, rank, dv], then back to token-major
         by_head = arena.take((hd, t, self.dv), ctx.dtype)
         ops.bmm(mixed.transpose(0, 1), self.w_uv_t, by_head)

@@ -129,7 +129,17 @@ class RoutedExperts(FeedForward):
     experts, plus, with ``shared_size``, a SwiGLU expert of that inner size that every token uses.
     Experts have no biases. Tensor names after the prefix: ``router``, ``e<i>.gate|up|down``,
     ``shared.gate|up|down`` (``names`` renames "router", "expert" (a format of the index), "shared",
-    "gate", "up", "down").
+    "gate", "up", "down", "correction", "shared_gate").
+
+    ``routing="scored"`` chooses differently: the scores are the softmax over ALL router outputs; the
+    choice takes the ``top`` largest of ``score + correction`` (``correction=True``: a tensor with one value
+    per output) and looks only inside the ``group_keep`` best of ``groups`` equal groups of neighbouring
+    outputs (a group's value is its largest choice score); the weights are the chosen scores (without the
+    correction) over their sum, times ``route_scale``. ``identity``: that many further router outputs after
+    the experts' are identity experts, whose output is the token's input itself; they take part in the
+    softmax, the groups and the choice, and have no tensors. ``shared_gate``: the shared expert's output is
+    multiplied by ``sigmoid(w_sg . x)``, one value per token (a ``[1, hidden]`` tensor, which rides along
+    in the router's product so that it is 32-bit like the router).
 
     The experts' matrices are stacked (``[E, 2 ff, hidden]`` gate rows then up rows, ``[E, hidden,
     ff]``); tokens are sorted by expert on the device and the products run tile by tile over that
@@ -137,12 +147,29 @@ class RoutedExperts(FeedForward):
     whatever the routing and can be recorded."""
 
     recordable = EVERY_STEP
-    _NAMES = {"router": "router", "expert": "e{}.", "shared": "shared.", "gate": "gate", "up": "up", "down": "down"}
+    _NAMES = {"router": "router", "expert": "e{}.", "shared": "shared.", "gate": "gate", "up": "up", "down": "down",
+              "correction": "correction", "shared_gate": "sg"}
 
     def __init__(self, prefix: str, hidden_size: int, num_experts: int, top: int, expert_size: int,
-                 shared_size: int | None = None, names: "Mapping[str, str] | None" = None) -> None:
-        if not 0 < top <= min(num_experts, 32):
-            raise ValueError(f"top={top} must be between 1 and min(num_experts={num_experts}, 32)")
+                 shared_size: int | None = None, names: "Mapping[str, str] | None" = None, routing: str = "top_logits",
+                 correction: bool = False, groups: int = 1, group_keep: int = 1, route_scale: float = 1.0,
+                 identity: int = 0, shared_gate: bool = False) -> None:
+        outputs = int(num_experts) + int(identity)
+        if not 0 < top <= min(outputs, 32):
+            raise ValueError(f"top={top} must be between 1 and min(router outputs={outputs}, 32)")
+        if routing not in ("top_logits", "scored"):
+            raise ValueError(f"routing={routing!r}: 'top_logits' or 'scored'")
+        if routing != "scored" and (correction or groups != 1 or identity or route_scale != 1.0):
+            raise ValueError("a correction, groups, identity experts and a constant on the weights come with routing='scored'")
+        if identity < 0 or not 1 <= groups <= 32 or outputs % groups or not 1 <= group_keep <= groups:
+            raise ValueError(f"groups={groups} (at most 32) must divide the {outputs} router outputs, and 1 <= group_keep <= groups")
+        if outputs // groups * group_keep < top:
+            raise ValueError(f"the {group_keep} kept groups of {outputs // groups} outputs hold fewer than top={top}")
+        if shared_gate and shared_size is None:
+            raise ValueError("a gate on the shared expert needs a shared expert")
+        self.scored, self.has_correction, self.groups, self.group_keep = routing == "scored", bool(correction), int(groups), int(group_keep)
+        self.route_scale, self.identity, self.shared_gate, self.outputs = float(route_scale), int(identity), bool(shared_gate), outputs
+        self.rule = ops.PLAIN_ROUTE
         if expert_size <= 0 or (shared_size is not None and shared_size <= 0):
             raise ValueError("expert sizes must be positive")
         self.prefix, self.h = prefix, int(hidden_size)
@@ -154,7 +181,13 @@ class RoutedExperts(FeedForward):
     def tensor_specs(self, prefix: str) -> list[TensorSpec]:
         p, n, h, ff, e = prefix + self.prefix, self.names, self.h, self.ff, self.experts
         each = [p + n["expert"].format(i) for i in range(e)]
-        specs = [TensorSpec(p + n["router"], (e, h)),
+        if self.shared_gate:
+            sg = p + n["shared"] + n["shared_gate"]
+            router = TensorSpec(p + n["router"] + "+" + n["shared"] + n["shared_gate"], (self.outputs + 1, h),
+                                merged_from=(p + n["router"], sg), merged_rows=(self.outputs, 1))
+        else:
+            router = TensorSpec(p + n["router"], (self.outputs, h))
+        specs = [router,
                  TensorSpec(p + "experts.gate+up", (e * 2 * ff, h),
                             merged_from=tuple(x + n[r] for x in each for r in ("gate", "up")), merged_rows=(ff,) * (2 * e)),
                  TensorSpec(p + "experts.down", (e * h, ff), merged_from=tuple(x + n["down"] for x in each),
@@ -164,11 +197,17 @@ class RoutedExperts(FeedForward):
             specs += [TensorSpec(sp + n["gate"] + "+" + n["up"], (2 * sf, h), merged_from=(sp + n["gate"], sp + n["up"]),
                                  merged_rows=(sf, sf)),
                       TensorSpec(sp + n["down"], (h, sf))]
+        if self.has_correction:
+            specs.append(TensorSpec(p + n["correction"], (self.outputs,), std=0.05))
         return specs
 
     def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
         p, n = prefix + self.prefix, self.names
-        self.w_router = tensors[p + n["router"]]
+        self.w_router = tensors[p + n["router"] + ("+" + n["shared"] + n["shared_gate"] if self.shared_gate else "")]
+        if self.scored:
+            corr = tensors[p + n["correction"]].float().contiguous() if self.has_correction else None
+            self.rule = ops.RouteRule(scored=True, groups=self.groups, keep=self.group_keep, scale=self.route_scale,
+                                      identity=self.identity, correction=corr)
         self.w_gate_up = tensors[p + "experts.gate+up"].view(self.experts, 2 * self.ff, self.h)
         self.w_down = tensors[p + "experts.down"].view(self.experts, self.h, self.ff)
         if self.shared_ff is not None:
@@ -181,7 +220,7 @@ class RoutedExperts(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         t, arena = x.shape[0], ctx.arena
         tile_rows = ops.moe_tile_rows(t, self.top, self.experts, ctx.dtype, (self.h, self.ff))
-        plan = ops.moe_route_from(x, self.w_router, self.top, self.counts, arena, tile_rows)
+        plan = ops.moe_route_from(x, self.w_router, self.top, self.counts, arena, tile_rows, self.rule, self.outputs)
         act = arena.take((t * self.top, self.ff), ctx.dtype)
         ops.moe_gemm(x, self.w_gate_up, act, plan, gated=True, gather=True, arena=arena)
         y = arena.take((t * self.top, self.h), ctx.dtype)
@@ -193,7 +232,8 @@ class RoutedExperts(FeedForward):
             shared = arena.take((t, self.h), ctx.dtype)
             ops.gemm(sact, self.ws_down, shared)
         out = arena.take((t, self.h), ctx.dtype)
-        ops.moe_combine(y, plan, shared, out)
+        ops.moe_combine(y, plan, shared, out, x=x if self.identity else None,
+                        shared_gate=plan["logits"][:, self.outputs] if self.shared_gate else None)
         return out
 
 

@@ -10,7 +10,8 @@ the result rounded once), ``unit_offset`` (the weight is stored around
 zero and the gain is ``1 + weight``; the whole norm is then 32-bit with one rounding), and
 ``PostRMSNorm``, a norm on a sub-layer's OUTPUT with an optional per-column layer scale, which
 is left pending on the stream and applied by the next norm's kernel in the same pass as the
-residual sum: ``x <- x + scale * norm(y)``, then ``norm(x)``.
+residual sum: ``x <- x + scale * norm(y)``, then ``norm(x)``; and ``LayerScale``, the per-column scale
+alone (``x <- x + scale * y``), pending in the same way.
 """
 
 from __future__ import annotations
@@ -106,5 +107,39 @@ class PostRMSNorm(Norm):
         raise NotImplementedError("a post norm is applied by the norm that follows it; use leave()")
 
 
+class LayerScale(Norm):
+    """No norm at all on a sub-layer's output, only a learned factor per column (tensor ``name``) and an
+    optional constant ``mult``: ``leave(stream, y)`` leaves ``y`` pending with the factor, and the next norm's
+    kernel adds ``mult * scale * y`` to the 32-bit stream in the same pass as its own norm."""
+
+    recordable = EVERY_STEP
+
+    def __init__(self, name: str, size: int, mult: float = 1.0) -> None:
+        self.name, self.size, self.mult = name, int(size), float(mult)
+        if self.mult != 1.0:
+            raise NotImplementedError("a layer scale with a constant beside it")
+        self.scale: torch.Tensor | None = None
+
+    def tensor_specs(self, prefix: str) -> list[TensorSpec]:
+        return [TensorSpec(prefix + self.name, (self.size,), init="one_plus_normal", std=0.1)]
+
+    def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.scale = tensors[prefix + self.name]
+
+    def leave(self, stream: ResidualStream, y: torch.Tensor) -> None:
+        if stream.delta is not None:
+            raise RuntimeError("a sub-layer output is already pending on the stream")
+        stream.delta = y
+        stream.post = (None, self.scale, 0.0, False, 1.0)
+        stream.sumsq = None
+
+    def forward(self, stream: ResidualStream, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError("a layer scale is applied by the norm that follows it; use leave()")
+
+    def forward_rows(self, stream, rows, num_rows, ctx):
+        raise NotImplementedError("a layer scale is applied by the norm that follows it; use leave()")
+
+
+register_norm("layer_scale", LayerScale)
 register_norm("rms_norm", RMSNorm)
 register_norm("post_rms_norm", PostRMSNorm)

@@ -32,6 +32,12 @@ arguments): ``q, k, v = silu(W_q h), silu(W_k h), silu(W_v h)``; per head ``S <-
 ``o = S^T q``; the concatenated heads are RMS-normed together with a plain weight, multiplied by
 ``sigmoid(W_g h)`` and projected by ``W_o``.
 
+``GatedLinearAttention``: linear attention with a decay per head, key channel and token:
+``q = W_q h * dim^-1/2``, ``k = W_k h``, ``v = W_v h``; ``alpha = sigmoid(W_a2 W_a1 h + b)^(1/tau)`` with a
+constant ``tau``; per head ``S <- diag(alpha) S + k v^T``, ``o = S^T q`` (the read-out sees the current
+token's write). Each head's ``o`` is RMS-normed with a weight shared by the heads, multiplied by
+``silu(W_g h)`` and projected by ``W_o``.
+
 Gates, decays, step sizes, unit scalings and the state are 32-bit; the projections and the
 convolution's inputs are in the model dtype. Nothing of a step is read on the host: requests are
 found through ``cu_query_lens`` and ``state_slots`` on the device, so every kind of step can be
@@ -366,6 +372,63 @@ class DecayLinearAttention(Mixer):
         return out
 
 
+class GatedLinearAttention(Mixer):
+    recordable = EVERY_STEP
+    _NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "decay_down": "a1", "decay_up": "a2", "decay_bias": "a2.b",
+              "norm": "norm", "out": "o"}
+
+    def __init__(self, prefix: str, hidden_size: int, num_heads: int, key_dim: int, value_dim: int, tau: float,
+                 norm_eps: float, decay_rank: int = -1, names: Mapping[str, str] | None = None) -> None:
+        """``decay_rank``: the inner size of the decay's low-rank pair; ``-1`` takes it from the
+        checkpoint (then the model cannot be drawn at random)."""
+        _check_key_dim("gated_linear_attention", key_dim)
+        if not tau > 0:
+            raise ValueError(f"tau={tau} must be positive")
+        self.prefix, self.h = prefix, int(hidden_size)
+        self.heads, self.d, self.dv = int(num_heads), int(key_dim), int(value_dim)
+        self.tau, self.eps, self.rank = float(tau), float(norm_eps), int(decay_rank)
+        self.names = {**self._NAMES, **(names or {})}
+
+    def cache_need(self) -> StateNeed:
+        return StateNeed((self.heads * self.d * self.dv,), torch.float32)
+
+    def tensor_specs(self, prefix: str) -> list[TensorSpec]:
+        p, n, h = prefix + self.prefix, self.names, self.h
+        qk, vv = self.heads * self.d, self.heads * self.dv
+        return [TensorSpec(p + "qkvg", (2 * qk + 2 * vv, h), merged_from=tuple(p + n[r] for r in ("q", "k", "v", "gate")),
+                           merged_rows=(qk, qk, vv, vv)),
+                TensorSpec(p + n["decay_down"], (self.rank, h)),
+                TensorSpec(p + n["decay_up"], (qk, self.rank)),
+                TensorSpec(p + n["decay_bias"], (qk,), std=1.0),
+                TensorSpec(p + n["norm"], (self.dv,), init="one_plus_normal"),
+                TensorSpec(p + n["out"], (h, vv))]
+
+    def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
+        p, n = prefix + self.prefix, self.names
+        self.w_in, self.norm_w, self.w_o = tensors[p + "qkvg"], tensors[p + n["norm"]], tensors[p + n["out"]]
+        self.w_a1, self.w_a2 = tensors[p + n["decay_down"]], tensors[p + n["decay_up"]]
+        self.decay_bias = tensors[p + n["decay_bias"]].float().contiguous()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: StateCacheEntry, writes_cache: bool, position: Any) -> torch.Tensor:
+        t, arena = x.shape[0], ctx.arena
+        qk, vv = self.heads * self.d, self.heads * self.dv
+        proj = arena.take((t, 2 * qk + 2 * vv), ctx.dtype)
+        ops.gemm(x, self.w_in, proj)
+        low = arena.take((t, self.w_a1.shape[0]), ctx.dtype)
+        ops.gemm(x, self.w_a1, low)
+        z = arena.take((t, qk), torch.float32)            # the decay's pre-activation leaves its product as 32-bit
+        ops.gemm(low, self.w_a2, z)
+        read = arena.take((t, self.heads, self.dv), torch.float32)
+        ops.linear_scan_gated(proj[:, :qk], proj[:, qk: 2 * qk], proj[:, 2 * qk: 2 * qk + vv], z, self.decay_bias, self.tau,
+                              self.d ** -0.5, cache.state, ctx, self.heads, self.d, self.dv, read)
+        gated = arena.take((t, vv), ctx.dtype)
+        ops.head_norm_gate(read, self.norm_w, False, proj[:, 2 * qk + vv:], True, self.eps, gated, gate_silu=True)
+        out = arena.take((t, self.h), ctx.dtype)
+        ops.gemm(gated, self.w_o, out)
+        return out
+
+
+register_mixer("gated_linear_attention", GatedLinearAttention)
 register_mixer("gated_delta", GatedDeltaMixer)
 register_mixer("time_mix", TimeMixMixer)
 register_mixer("decay_linear_attention", DecayLinearAttention)

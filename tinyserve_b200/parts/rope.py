@@ -4,7 +4,9 @@ Formula (upstream src/tinyserve/layers.py:61-65): ``inv_freq[i] = theta ** (-2i 
 in float64, ``angle = position * inv_freq`` in float64, cos and sin taken in float64 and
 rounded to float32. The rotation itself (pairs ``i`` and ``i + rotary_dim/2`` for the "half"
 pairing, neighbours ``2i, 2i+1`` for "interleaved"; src/tinyserve/layers.py:84-91 has the
-former) is applied by the mixer's fused kernel, which receives these tables.
+former) is applied by the mixer's fused kernel, which receives these tables. ``scaling``: the four
+keys of the rule by wavelength below, or ``{"factor": f}`` alone for linear scaling (every
+frequency divided by ``f``).
 """
 
 from __future__ import annotations
@@ -48,7 +50,13 @@ class RotaryEncoding(PositionEncoding):
         two_i = torch.arange(0, self.rotary_dim, 2, dtype=torch.float64)
         self._inv_freq_host = self.theta ** (-two_i / self.rotary_dim)
         self.scaling = None
-        if scaling:
+        if scaling and set(scaling) == {"factor"}:
+            # linear scaling: every frequency divided by the factor (positions stretched by it)
+            if not float(scaling["factor"]) > 0:
+                raise ValueError(f"rotary scaling factor must be positive, got {scaling['factor']}")
+            self.scaling = ("linear", float(scaling["factor"]))
+            self._inv_freq_host = self._inv_freq_host / self.scaling[1]
+        elif scaling:
             self.scaling = tuple(float(scaling[k]) for k in ("factor", "low", "high", "original"))
             self._inv_freq_host = scale_by_wavelength(self._inv_freq_host, *self.scaling)
         self._inv_freq: torch.Tensor | None = None
