@@ -238,7 +238,7 @@ def latent_prepare(q_in, q_folded, ckr, norm_weight, eps, cos, sin, rotary_dim, 
     q_out.copy_(torch.cat([q_folded.float().transpose(0, 1), qr], -1).to(q_out.dtype))
 
 
-def latent_attention(q, cache, page_size, block_tables, ctx: Any, rank, scale, window, out) -> None:
+def latent_attention(q, cache, page_size, block_tables, ctx: Any, rank, scale, window, out, sinks=None) -> None:
     t, heads, d = q.shape
     res = torch.zeros(t, heads, rank, dtype=torch.float32, device=q.device)
     cu = ctx.cu_query_lens.tolist()
@@ -253,7 +253,10 @@ def latent_attention(q, cache, page_size, block_tables, ctx: Any, rank, scale, w
         if window:
             hidden = hidden | (pos[None, :] <= qpos[:, None] - window)
         s = torch.einsum("ihd,jd->hij", q[r0: r0 + n].float(), rows) * scale
-        p = torch.softmax(s.masked_fill(hidden, float("-inf")), -1)
+        s = s.masked_fill(hidden, float("-inf"))
+        if sinks is not None:        # one more column per head whose value is zero
+            s = torch.cat([s, sinks.float().view(heads, 1, 1).expand(heads, n, 1)], -1)
+        p = torch.softmax(s, -1)[:, :, : rows.shape[0]]
         res[r0: r0 + n] = torch.einsum("hij,jd->ihd", p, rows[:, :rank])
     out.copy_(res.to(out.dtype))
 
@@ -276,26 +279,47 @@ def moe_tile_rows(num_tokens, top, experts, dtype, widths) -> int:
     return 64
 
 
-def moe_route_from(x, w_router, top, counts, arena=None, tile_rows=64) -> dict:
-    return moe_route(x.float() @ w_router.float().t(), top, counts, arena, tile_rows)
+def moe_route_from(x, w_router, top, counts, arena=None, tile_rows=64, rule=None, outputs=None) -> dict:
+    return moe_route(x.float() @ w_router.float().t(), top, counts, arena, tile_rows, rule, outputs)
 
 
-def moe_route(logits, top, counts, arena=None, tile_rows=64) -> dict:
-    """The same plan as the kernels make, with the rows of an expert in token order."""
-    t, e = logits.shape
-    # value down, index up: a stable sort of the negated logits
-    order = torch.sort(-logits.float(), dim=-1, stable=True).indices[:, :top]
-    best = torch.gather(logits.float(), 1, order)
-    weights = torch.softmax(best, -1)
+def moe_route(logits, top, counts, arena=None, tile_rows=64, rule=None, outputs=None) -> dict:
+    """The same plan as the kernels make, with the rows of an expert in token order. ``rule``: an object with
+    ``scored, groups, keep, scale, identity, correction`` (None: the largest logits, soft-maxed alone)."""
+    t = logits.shape[0]
+    e = logits.shape[1] if outputs is None else outputs
+    z = logits[:, :e].float()
+    identity = 0
+    if rule is None or not rule.scored:
+        # value down, index up: a stable sort of the negated logits
+        order = torch.sort(-z, dim=-1, stable=True).indices[:, :top]
+        weights = torch.softmax(torch.gather(z, 1, order), -1)
+    else:
+        identity = rule.identity
+        scores = torch.exp(z - z.max(-1, keepdim=True).values)
+        scores = scores / scores.sum(-1, keepdim=True)
+        choice = scores if rule.correction is None else scores + rule.correction.float()
+        if rule.groups > 1:
+            best = choice.view(t, rule.groups, -1).max(-1).values
+            kept = torch.sort(-best, dim=-1, stable=True).indices[:, : rule.keep]
+            allowed = torch.zeros(t, rule.groups, dtype=torch.bool, device=z.device).scatter_(1, kept, True)
+            choice = choice.masked_fill(~allowed.repeat_interleave(e // rule.groups, dim=1), float("-inf"))
+        order = torch.sort(-choice, dim=-1, stable=True).indices[:, :top]
+        picked = torch.gather(scores, 1, order)
+        weights = picked / (picked.sum(-1, keepdim=True) + 1e-20) * rule.scale
+    real = e - identity
     ids = order.reshape(-1)
-    by_expert = torch.sort(ids, stable=True).indices                 # sorted row -> pick
-    row_of = torch.empty_like(by_expert)
-    row_of[by_expert] = torch.arange(ids.numel(), device=ids.device)
-    sizes = torch.bincount(ids, minlength=e)
+    queued = torch.nonzero(ids < real).reshape(-1)                     # picks of experts with matrices
+    by_expert = queued[torch.sort(ids[queued], stable=True).indices]   # sorted row -> pick
+    row_of = torch.full_like(ids, -1)
+    row_of[by_expert] = torch.arange(by_expert.numel(), device=ids.device)
+    token_of = torch.zeros_like(ids)
+    token_of[: by_expert.numel()] = by_expert // top
+    sizes = torch.bincount(ids[queued], minlength=real)
     offsets = torch.cat([sizes.new_zeros(1), sizes.cumsum(0)])
-    return {"top": top, "experts": e, "picks": ids.numel(), "ids": ids.int(), "weights": weights.reshape(-1),
-            "row_of": row_of.int(), "token_of": (by_expert // top).int(), "offsets": offsets.int(),
-            "max_tiles": moe_max_tiles(t, top, e, tile_rows), "tile_rows": tile_rows}
+    return {"top": top, "experts": real, "picks": ids.numel(), "ids": ids.int(), "weights": weights.reshape(-1),
+            "row_of": row_of.int(), "token_of": token_of.int(), "offsets": offsets.int(), "logits": logits, "identity": identity,
+            "max_tiles": moe_max_tiles(t, top, real, tile_rows), "tile_rows": tile_rows}
 
 
 def moe_gemm(x, w, out, plan, gated, gather, arena=None) -> None:
@@ -310,12 +334,16 @@ def moe_gemm(x, w, out, plan, gated, gather, arena=None) -> None:
             out[off[e]: off[e + 1]] = z.to(out.dtype)
 
 
-def moe_combine(y, plan, shared_out, out) -> None:
+def moe_combine(y, plan, shared_out, out, x=None, shared_gate=None) -> None:
     t, top = out.shape[0], plan["top"]
-    picked = y[plan["row_of"].long()].float().reshape(t, top, -1)
+    rows = plan["row_of"].long()
+    picked = y[rows.clamp(min=0)].float().reshape(t, top, -1)
+    if x is not None:                       # an identity pick's output is the token's input
+        picked = torch.where((rows < 0).reshape(t, top, 1), x.float().reshape(t, 1, -1), picked)
     total = (picked * plan["weights"].reshape(t, top, 1)).sum(1)
     if shared_out is not None:
-        total = total + shared_out.float()
+        g = 1.0 if shared_gate is None else torch.sigmoid(shared_gate.float()).reshape(t, 1)
+        total = total + g * shared_out.float()
     out.copy_(total.to(out.dtype))
 
 
@@ -392,14 +420,16 @@ def causal_conv_silu(x, taps, state, ctx, out) -> None:
 
 
 def qkv_prepare(q_in, k_in, v_in, q_weight, k_weight, eps, cos, sin, rotary_dim, slots, k_cache, v_cache, page_size,
-                heads, kv_heads, d, dv, q_out, q_bias=None, k_bias=None, v_bias=None) -> None:
+                heads, kv_heads, d, dv, q_out, q_bias=None, k_bias=None, v_bias=None, norm_whole=False) -> None:
     t = q_out.shape[0]
 
     def prep(x, w, n, bias=None):
         y = x.float().reshape(t, n, d)
         if bias is not None:
             y = y + bias.float().view(n, d)
-        if w is not None:
+        if w is not None and norm_whole:        # one root mean square over all heads, a weight per element
+            y = y * torch.rsqrt(y.pow(2).mean((-2, -1), keepdim=True) + eps) * w.float().view(n, d)
+        elif w is not None:
             y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * w.float()
         return _rotate(y, cos, sin, rotary_dim, False)
 
@@ -448,6 +478,27 @@ def linear_scan_decay(q, k, v, decay, state, ctx, heads, d, dv, out) -> None:
                 S = decay[h] * S + torch.outer(kk, vv)
                 out[t, h] = S.t() @ qq
             st[h] = S
+
+
+def linear_scan_gated(q, k, v, w_pre, w_bias, tau, q_scale, state, ctx, heads, d, dv, out) -> None:
+    cu, slots = ctx.cu_query_lens.tolist(), ctx.state_slots.tolist()
+    for b in range(ctx.num_seqs):
+        st = state[slots[b]].view(heads, d, dv)
+        for h in range(heads):
+            S = st[h].clone()
+            for t in range(cu[b], cu[b + 1]):
+                qq, kk = q[t, h * d: (h + 1) * d].to(state.dtype) * q_scale, k[t, h * d: (h + 1) * d].to(state.dtype)
+                vv = v[t, h * dv: (h + 1) * dv].to(state.dtype)
+                z = w_pre[t, h * d: (h + 1) * d] + w_bias[h * d: (h + 1) * d]
+                alpha = torch.exp(torch.nn.functional.logsigmoid(z.to(state.dtype)) / tau)
+                S = alpha[:, None] * S + torch.outer(kk, vv)
+                out[t, h] = S.t() @ qq
+            st[h] = S
+
+
+def rms_norm_rows(x, weight, eps, out) -> None:
+    y = x.float()
+    out.copy_((y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(out.dtype))
 
 
 def token_shift_mix(x, mu, state, ctx, out) -> None:
@@ -568,7 +619,8 @@ _NAMES = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_writ
           "head_norm_gate", "mlstm_scan", "delta_scan", "causal_conv_silu", "qkv_prepare", "gemm_gated",
           "post_norm_add_rms_norm", "latent_prepare", "latent_attention", "bmm", "transpose01", "moe_max_tiles", "moe_tile_rows", "moe_route_from",
           "moe_route", "moe_gemm", "moe_combine", "linear_scan_bonus", "linear_scan_decay", "token_shift_mix",
-          "embed_pos_norm", "stream_sum", "add_bias", "tanh_", "act_mul_gather", "gemm_biased_swiglu"]
+          "embed_pos_norm", "stream_sum", "add_bias", "tanh_", "act_mul_gather", "gemm_biased_swiglu", "linear_scan_gated",
+          "rms_norm_rows"]
 
 
 @contextmanager

@@ -221,3 +221,11 @@ def forward(cfg: Mapping[str, Any], w: Mapping[str, torch.Tensor], tokens: list[
         if streams is not None:
             streams.append(x.clone())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def greedy(cfg: Mapping[str, Any], w: Mapping[str, torch.Tensor], prompt: list[int], new_tokens: int) -> list[int]:
+    """Greedy continuation, recomputing the whole sequence for every token."""
+    toks = list(prompt)
+    for _ in range(new_tokens):
+        toks.append(int(forward(cfg, w, toks)[-1].argmax()))
+    return toks[len(prompt):]
