@@ -1,4 +1,4 @@
-"""``python bench.py --designs [--design fegilix|guzovik|gasavik]``: prefill and decode throughput of a
+"""``python bench.py --designs [--design fegilix|guzovik|gasavik|diderax]``: prefill and decode throughput of a
 design at layer sizes that resemble a real model's (random weights), beside the dense Qwen3 decoder,
 the closest existing model, with the same width, attention heads, (active) feed-forward size and
 number of layers; and where each design's step time goes, kernel class by kernel class, with the
@@ -85,11 +85,33 @@ def gasavik_config(s: dict) -> dict:
             "residual_mult": 0.5, "token_side": {"dim": 256}, "layers": [par, wkv, wkv, delta, par, wkv]}
 
 
-DESIGNS = {"fegilix": fegilix_config, "guzovik": guzovik_config, "gasavik": gasavik_config}
+def diderax_config(s: dict) -> dict:
+    """Attention whose values are the keys + biased feed-forward, gated linear attention + routed experts, gated
+    linear attention + feed-forward, latent attention with a query latent + routed experts, attention + feed-forward,
+    gated linear attention + routed experts. Three of the router's outputs are used per token (experts of a quarter
+    of the dense feed-forward's size, or one of four identity experts) beside a gated shared expert of that size;
+    latents of 512 + 64 for keys and values and of three eighths of the width for the queries; linear-attention
+    heads of 128 that fill the width."""
+    attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+            "rot": {"dims": s["dim"] // 2, "base": 250000.0, "scaling": {"factor": 8.0}}}
+    latent = {"heads": s["heads"], "dim": s["dim"], "rot_dim": 64, "vdim": s["dim"], "kv_rank": 512, "q_rank": 3 * s["width"] // 8,
+              "scale": (s["dim"] + 64) ** -0.5, "rot": {"dims": 64, "base": 250000.0}}
+    gla = {"heads": s["rec_heads"], "dim": s["dim"], "vdim": s["dim"], "tau": 16.0, "decay_rank": 64}
+    ff = s["ff"] // 4
+    moe = {"kind": "moe", "router": {"experts": s["experts"], "identity": 4, "top": 3, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": ff}, "shared": {"ff": ff}}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    return {"architecture": "Diderax", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-6}, "max_positions": 8192,
+            "layers": [{"type": "attention", "mlp": dense, "mixer": attn}, {"type": "gla", "mlp": moe, "mixer": gla},
+                       {"type": "gla", "mlp": dense, "mixer": gla}, {"type": "latent_attention", "mlp": moe, "mixer": latent},
+                       {"type": "attention", "mlp": dense, "mixer": attn}, {"type": "gla", "mlp": moe, "mixer": gla}]}
+
+
+DESIGNS = {"fegilix": fegilix_config, "guzovik": guzovik_config, "gasavik": gasavik_config, "diderax": diderax_config}
 NEW_OPS = ["post_norm_add_rms_norm", "latent_prepare", "latent_attention", "bmm", "transpose01", "moe_route_from", "moe_route", "moe_gemm",
            "moe_combine", "gemm_gated", "hc_mix_norm", "hc_collapse", "act_mul", "softcap", "head_norm_gate", "mlstm_scan", "delta_scan",
            "causal_conv_silu", "qkv_prepare", "linear_scan_bonus", "linear_scan_decay", "token_shift_mix", "embed_pos_norm",
-           "stream_sum", "add_bias", "tanh_", "act_mul_gather", "gemm_biased_swiglu"]
+           "stream_sum", "add_bias", "tanh_", "act_mul_gather", "gemm_biased_swiglu", "linear_scan_gated", "rms_norm_rows"]
 OLD_OPS = ["embed", "add_rms_norm", "rope_tables", "silu_mul", "qk_norm_rope_write", "paged_attention",
            "decode_attention_fused", "gemm", "gemm_swiglu", "gemm_to_stream", "gemm_normed", "sample"]
 
@@ -223,6 +245,11 @@ class DesignBench(Bench):
             if name == "linear_scan_decay":   # 4 flops per state element and token
                 ctx, heads, d, dv = a[5], a[6], a[7], a[8]
                 return (2.0 * ctx.num_seqs * heads * d * dv * 4 + nbytes(a[0], a[1], a[2], a[9]), 4.0 * a[0].shape[0] * heads * d * dv)
+            if name == "linear_scan_gated":   # state in and out, q, k, v and the decays' pre-activations read, the read-out written; 4 flops per state element and token
+                ctx, heads, d, dv = a[8], a[9], a[10], a[11]
+                return (2.0 * ctx.num_seqs * heads * d * dv * 4 + nbytes(a[0], a[1], a[2], a[3], a[12]), 4.0 * a[0].shape[0] * heads * d * dv)
+            if name == "rms_norm_rows":
+                return 2.0 * nbytes(a[3]), 0.0
             if name == "token_shift_mix":
                 return nbytes(a[0], a[4]), 0.0
             if name == "stream_sum":          # the stream read and written, every term read, the copy written

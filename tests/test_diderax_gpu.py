@@ -297,6 +297,45 @@ def test_combine_with_identity_picks_and_a_gated_shared_expert_kernel(dtype, tok
         torch.testing.assert_close(got.float(), want.float(), **_tol(dtype))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens, experts, identity, top, hidden, ff", [(9, 4, 2, 3, 64, 24), (300, 6, 2, 3, 128, 64), (700, 8, 4, 3, 256, 256),
+                                                                        (1500, 4, 12, 4, 512, 256)])
+def test_experts_with_identity_picks_from_routing_to_combine(dtype, tokens, experts, identity, top, hidden, ff) -> None:
+    """The whole mixture against the references, at sizes that take each form of the experts' products (the largest
+    ones sort and gather the rows for tiles of 128): rows of the sorted order that no pick owns are never looked up."""
+    from tinyserve_b200.kernels import ops
+
+    outputs = experts + identity
+    x = _rand(tokens, hidden, seed=1, dtype=dtype)
+    w_router = _rand(outputs + 1, hidden, seed=2, scale=0.3, dtype=dtype)
+    w_gu, w_down = _rand(experts, 2 * ff, hidden, seed=3, scale=0.1, dtype=dtype), _rand(experts, hidden, ff, seed=4, scale=0.1, dtype=dtype)
+    shared = _rand(tokens, hidden, seed=5, dtype=dtype)
+    rule = ops.RouteRule(scored=True, groups=2, keep=1, scale=1.5, identity=identity, correction=_rand(outputs, seed=6, scale=0.05))
+    res = []
+    for impl in (ops, refs):
+        arena = Arena()
+        counts = torch.zeros(experts, dtype=torch.int32, device="cuda")
+        tile_rows = impl.moe_tile_rows(tokens, top, experts, dtype, (hidden, ff))
+        plan = impl.moe_route_from(x, w_router, top, counts, arena, tile_rows, rule, outputs)
+        act = torch.full((tokens * top, ff), float("nan"), dtype=dtype, device="cuda")
+        impl.moe_gemm(x, w_gu, act, plan, gated=True, gather=True, arena=arena)
+        y = torch.full((tokens * top, hidden), float("nan"), dtype=dtype, device="cuda")
+        impl.moe_gemm(act, w_down, y, plan, gated=False, gather=False, arena=arena)
+        out = torch.empty(tokens, hidden, dtype=dtype, device="cuda")
+        impl.moe_combine(y, plan, shared, out, x=x, shared_gate=plan["logits"][:, outputs])
+        res.append((out.float(), plan))
+    (got, plan), (want, ref_plan) = res
+    assert not got.isnan().any()
+    if dtype == torch.float32:
+        assert torch.equal(plan["ids"], ref_plan["ids"])
+        torch.testing.assert_close(got, want, atol=2e-4, rtol=2e-4)
+    else:
+        same = (plan["ids"].view(tokens, top) == ref_plan["ids"].view(tokens, top)).all(-1)      # rounding may flip a close call
+        assert float(same.float().mean()) > 0.97
+        torch.testing.assert_close(got[same], want[same], atol=2e-2 * float(want.abs().max()), rtol=6e-2)     # bfloat16 steps at the outputs' size
+    assert bool((plan["ids"] >= experts).any()) and bool((plan["ids"] < experts).any())
+
+
 # ------------------------------------------------------------------- whole models
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):

@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(TG_THREADS) gemm_tcgen05_kernel(const __grid_c
   constexpr int BN_OUT = SWIGLU ? BN / 2 : BN;          // output columns per tile
   const bool grouped = grp.tile_expert != nullptr;
   if (grouped) pdl_wait();            // the list of tiles is the work of the kernels before this one
-  const int tiles_m = grouped ? *grp.num_tiles : (M + TG_BM - 1) / TG_BM, tiles_n = (N + BN_OUT - 1) / BN_OUT;
+  const int tiles_m = grouped ? *(const volatile int*)grp.num_tiles : (M + TG_BM - 1) / TG_BM, tiles_n = (N + BN_OUT - 1) / BN_OUT;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + TG_BK - 1) / TG_BK;
 

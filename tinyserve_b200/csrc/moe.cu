@@ -253,7 +253,7 @@ __global__ void __launch_bounds__(SG_THREADS) moe_gemm_simt_kernel(
   pdl_trigger();
   pdl_wait();
   const int tile = blockIdx.y;
-  if (tile >= *num_tiles) return;
+  if (tile >= *(const volatile int*)num_tiles) return;      // volatile: never read in front of the wait
   const int e = tile_expert[tile], r0 = tile_row0[tile], rend = offsets[e + 1];
   const int n0 = blockIdx.x * SG_N;
   const T* we = w + (size_t)e * (GATED ? 2 : 1) * N * K;
@@ -360,7 +360,7 @@ __global__ void __launch_bounds__(TG_THREADS) moe_gemm_mma_kernel(
   pdl_trigger();
   pdl_wait();
   const int tile = blockIdx.y;
-  if (tile >= *num_tiles) return;
+  if (tile >= *(const volatile int*)num_tiles) return;      // volatile: never read in front of the wait
   const int e = tile_expert[tile], r0 = tile_row0[tile], rend = offsets[e + 1];
   const int n0 = blockIdx.x * TG_N;
   const bf16* we = w + (size_t)e * NB * N * K;
@@ -452,13 +452,19 @@ __global__ void __launch_bounds__(TG_THREADS) moe_gemm_mma_kernel(
 
 // ------------------------------------------------------------------------ gather
 // xs[row, :] = x[token_of[row], :] in pieces of 16 bytes (for the product that takes its rows in the sorted order).
+// Only the first *total_rows rows of the sorted order exist (picks of identity experts take none): the rows behind
+// them are zero-filled, and token_of is not read there.
+// (*total_rows is written two kernels back in the chain. It is read through a volatile pointer: a plain read of a
+// const __restrict__ pointer may be moved in front of the wait by the compiler, where a kernel that started early
+// sees the value of the step before.)
 __global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __restrict__ token_of, uint4* __restrict__ xs,
-                                  int picks, int pieces) {
+                                  int picks, int pieces, const int* total_rows) {
   pdl_trigger();
   pdl_wait();
+  const size_t live = (size_t)min(*(const volatile int*)total_rows, picks);
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < (size_t)picks * pieces; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t row = idx / pieces;
-    xs[idx] = x[(size_t)token_of[row] * pieces + (idx - row * pieces)];
+    xs[idx] = row < live ? x[(size_t)token_of[row] * pieces + (idx - row * pieces)] : make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
@@ -634,13 +640,16 @@ extern "C" int ts_moe_gemm(const void* x, const int* token_of, const void* w, vo
   return TS_ERR_BAD_ARGUMENT;
 }
 
-extern "C" int ts_moe_gather(const void* x, const int* token_of, void* xs, int picks, int row_bytes, cudaStream_t stream) {
+// total_rows: one int on the device, the rows of the sorted order that exist (offsets[experts] of the plan).
+extern "C" int ts_moe_gather(const void* x, const int* token_of, void* xs, int picks, int row_bytes, const int* total_rows,
+                             cudaStream_t stream) {
   if (picks <= 0) return 0;
+  if (!total_rows) return TS_ERR_BAD_ARGUMENT;
   if (row_bytes <= 0 || row_bytes % 16 != 0 || (((uintptr_t)x | (uintptr_t)xs) & 15)) return TS_ERR_UNSUPPORTED;
   const int pieces = row_bytes / 16;
   size_t blocks = ((size_t)picks * pieces + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  return launch(moe_gather_kernel, (int)blocks, 256, 0, stream, (const uint4*)x, token_of, (uint4*)xs, picks, pieces);
+  return launch(moe_gather_kernel, (int)blocks, 256, 0, stream, (const uint4*)x, token_of, (uint4*)xs, picks, pieces, total_rows);
 }
 
 // x [T, hidden] (the tokens' inputs) is read for identity picks (row_of < 0) and may be null when there are none;

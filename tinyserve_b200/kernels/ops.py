@@ -89,7 +89,7 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_latent_attention_mma_takes": [_i, _i],
     "ts_moe_route": [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp],
     "ts_moe_route_fused": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp],
-    "ts_moe_gather": [_vp, _vp, _vp, _i, _i, _vp],
+    "ts_moe_gather": [_vp, _vp, _vp, _i, _i, _vp, _vp],
     "ts_moe_gemm_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp],
     "ts_moe_gemm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "ts_moe_combine": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp],
@@ -1770,8 +1770,9 @@ def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: dict[str
             raise KernelError("moe_gemm: tiles of 128 rows are for bfloat16, with scratch for the gathered rows")
         if gather:
             xs = arena.take((picks, k), x.dtype)
+            total_rows = plan["offsets"][e:]          # the rows of the sorted order that exist: identity picks take none
             _check(_fn("ts_moe_gather")(_dev(x, "x"), plan["token_of"].data_ptr(), _dev(xs, "xs"), picks, k * x.element_size(),
-                                        _stream()), "moe_gather")
+                                        total_rows.data_ptr(), _stream()), "moe_gather")
             x = xs
         _check(_fn("ts_moe_gemm_tcgen05")(
             _dev(x, "x"), _dev(w, "w"), _dev(out, "out"), picks, n, k, e, int(bool(gated)), plan["offsets"].data_ptr(),
