@@ -36,10 +36,12 @@ def add_rms_norm(resid, delta, weight, eps, out, rows=None) -> None:
 
 
 def post_norm_add_rms_norm(resid, delta, post_weight, layer_scale, post_eps, post_offset, weight, offset, eps, out,
-                           rows=None, post_mult=1.0) -> None:
+                           rows=None, post_mult=1.0, delta_bias=None) -> None:
     x = resid if rows is None else resid[rows.long()]
     if delta is not None:
         y = (delta if rows is None else delta[rows.long()]).float()
+        if delta_bias is not None:
+            y = y + delta_bias.float()
         if post_weight is not None:
             g = post_weight.float()
             y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + post_eps) * (1 + g if post_offset else g) * post_mult

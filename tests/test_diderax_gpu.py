@@ -118,13 +118,16 @@ def test_layer_scale_pending_kernel(dtype, rows, hidden) -> None:
 
     x, y = _rand(rows, hidden, seed=1, scale=2.0), _rand(rows, hidden, seed=2, scale=3.0, dtype=dtype)
     ls, w = (1 + _rand(hidden, seed=3, scale=0.3)).to(dtype), (1 + _rand(hidden, seed=4, scale=0.3)).to(dtype)
-    got_x, want_x = x.clone(), x.clone()
-    got, want = torch.empty(rows, hidden, dtype=dtype, device="cuda"), torch.empty(rows, hidden, dtype=dtype, device="cuda")
-    ops.post_norm_add_rms_norm(got_x, y, None, ls, 0.0, False, w, False, 1e-6, got)
-    refs.post_norm_add_rms_norm(want_x, y, None, ls, 0.0, False, w, False, 1e-6, want)
-    torch.testing.assert_close(got_x, want_x, atol=1e-5, rtol=1e-5)
-    torch.testing.assert_close(got_x, x + ls.float() * y.float(), atol=1e-5, rtol=1e-5)
-    torch.testing.assert_close(got.float(), want.float(), **_tol(dtype))
+    bias = _rand(hidden, seed=5, dtype=dtype)
+    for b in (None, bias):              # the sub-layer's output bias rides along with the pending output
+        got_x, want_x = x.clone(), x.clone()
+        got, want = torch.empty(rows, hidden, dtype=dtype, device="cuda"), torch.empty(rows, hidden, dtype=dtype, device="cuda")
+        ops.post_norm_add_rms_norm(got_x, y, None, ls, 0.0, False, w, False, 1e-6, got, delta_bias=b)
+        refs.post_norm_add_rms_norm(want_x, y, None, ls, 0.0, False, w, False, 1e-6, want, delta_bias=b)
+        torch.testing.assert_close(got_x, want_x, atol=1e-5, rtol=1e-5)
+        added = y.float() if b is None else y.float() + b.float()
+        torch.testing.assert_close(got_x, x + ls.float() * added, atol=1e-5, rtol=1e-5)
+        torch.testing.assert_close(got.float(), want.float(), **_tol(dtype))
 
 
 def _sink_case(dtype, heads, rank, rot, page, lens, news, sinks, far=None):

@@ -3,6 +3,8 @@
 //
 //   y   = d / sqrt(mean(d^2) + eps_post) * gain(post_weight) * layer_scale * m  (when a post norm is pending;
 //                                                                                  m a constant multiplier)
+//   y   = (d + bias) * layer_scale                                               (a layer scale alone, with the
+//                                                                                  sub-layer's output bias, if any)
 //   x  <- x + y                                                                   (written back unless `rows`)
 //   out = x / sqrt(mean(x^2) + eps) * gain(weight)
 //
@@ -20,6 +22,7 @@ struct PostNormArgs {
   const void* delta;        // may be null: nothing pending
   const void* post_weight;  // may be null: the pending output is added as it is
   const void* layer_scale;  // may be null
+  const void* delta_bias;   // may be null: one value per column added to the pending output (only without a post norm)
   const void* weight;
   void* out;
   const int* rows;
@@ -43,6 +46,7 @@ __global__ void post_norm_add_rms_norm_kernel(PostNormArgs a) {
   const T* d = a.delta ? (const T*)a.delta + (size_t)row * hidden : nullptr;
   const T* pw = (const T*)a.post_weight;
   const T* ls = (const T*)a.layer_scale;
+  const T* db = (const T*)a.delta_bias;
   const T* w = (const T*)a.weight;
   const bool write_back = (a.rows == nullptr) && (d != nullptr);
   float post_rstd = 1.f;
@@ -70,6 +74,12 @@ __global__ void post_norm_add_rms_norm_kernel(PostNormArgs a) {
         for (int e = 0; e < VEC; ++e) y[e] = xs[i + e] * post_rstd * (a.post_offset ? 1.f + g[e] : g[e]) * a.post_mult;
       } else {
         if constexpr (VEC == 4) Quad<T>::load(d + i, y); else y[0] = to_float(d[i]);
+        if (db) {
+          float b[VEC];
+          if constexpr (VEC == 4) Quad<T>::load(db + i, b); else b[0] = to_float(db[i]);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) y[e] += b[e];
+        }
       }
       if (ls) {
         float s[VEC];
@@ -104,19 +114,20 @@ using namespace ts;
 
 extern "C" int ts_post_norm_add_rms_norm(float* resid, const void* delta, const void* post_weight, const void* layer_scale,
                                          float post_eps, int post_offset, float post_mult, const void* weight, int offset,
-                                         float eps, void* out, const int* rows, int num_rows, int hidden, int dtype,
-                                         cudaStream_t stream) {
+                                         float eps, void* out, const int* rows, int num_rows, int hidden, const void* delta_bias,
+                                         int dtype, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   if (hidden <= 0 || hidden > 12288 || !weight || !out || !resid) return TS_ERR_BAD_ARGUMENT;
   if (dtype != TS_DTYPE_F32 && dtype != TS_DTYPE_BF16) return TS_ERR_BAD_ARGUMENT;
-  if ((post_weight || layer_scale) && !delta) return TS_ERR_BAD_ARGUMENT;
+  if ((post_weight || layer_scale || delta_bias) && !delta) return TS_ERR_BAD_ARGUMENT;
+  if (delta_bias && post_weight) return TS_ERR_UNSUPPORTED;
   PostNormArgs a;
-  a.resid = resid; a.delta = delta; a.post_weight = post_weight; a.layer_scale = layer_scale; a.weight = weight;
+  a.resid = resid; a.delta = delta; a.post_weight = post_weight; a.layer_scale = layer_scale; a.delta_bias = delta_bias; a.weight = weight;
   a.out = out; a.rows = rows; a.num_rows = num_rows; a.hidden = hidden; a.post_eps = post_eps; a.eps = eps;
   a.post_offset = post_offset; a.offset = offset; a.post_mult = post_mult;
   const size_t smem = sizeof(float) * (size_t)hidden;
   const bool aligned = hidden % 4 == 0 &&
-      (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)post_weight | (uintptr_t)layer_scale | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
+      (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)post_weight | (uintptr_t)layer_scale | (uintptr_t)delta_bias | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
   const int per = aligned ? 4 : 1;
   int threads = 64;
   while (threads < 512 && threads * per * 2 <= hidden) threads <<= 1;

@@ -36,15 +36,29 @@ template <> struct Pair<bf16> {
   static constexpr uintptr_t MASK = 3;
 };
 
-// 1 / sqrt(mean(x^2) + eps) over a whole projection row of n elements (bias added first), by one warp.
+// The sum of squares of a whole projection row of n elements (bias added first), by all threads of the CTA.
 template <typename T>
-__device__ __forceinline__ float whole_rstd(const T* __restrict__ x, const T* __restrict__ bias, int n, float eps, int lane) {
+__device__ __forceinline__ float row_sumsq(const T* __restrict__ x, const T* __restrict__ bias, int n, float* scratch) {
   float ss = 0.f;
-  for (int i = lane; i < n; i += 32) {
-    const float v = to_float(x[i]) + (bias ? to_float(bias[i]) : 0.f);
-    ss = fmaf(v, v, ss);
+  if ((n & 1) == 0 && ((((uintptr_t)x) | ((uintptr_t)bias)) & Pair<T>::MASK) == 0) {
+    for (int i = 2 * threadIdx.x; i < n; i += 2 * blockDim.x) {
+      float a, b;
+      Pair<T>::load(x + i, a, b);
+      if (bias) {
+        float ba, bb;
+        Pair<T>::load(bias + i, ba, bb);
+        a += ba;
+        b += bb;
+      }
+      ss = fmaf(a, a, fmaf(b, b, ss));
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const float v = to_float(x[i]) + (bias ? to_float(bias[i]) : 0.f);
+      ss = fmaf(v, v, ss);
+    }
   }
-  return rsqrtf(warp_sum(ss) / (float)n + eps);
+  return block_sum(ss, scratch);
 }
 
 // One head by one warp: the head is read once from global memory into the warp's row of shared
@@ -56,8 +70,7 @@ __device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const 
                                                  const T* __restrict__ w, float eps,
                                                  const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                  int rotary_dim, int d, T* __restrict__ dst, int lane,
-                                                 float* __restrict__ row, const T* __restrict__ whole = nullptr,
-                                                 const T* __restrict__ whole_bias = nullptr, int whole_n = 0) {
+                                                 float* __restrict__ row, float given_rstd = -1.f) {
   const bool pairs = (d & 1) == 0 &&
       ((((uintptr_t)x) | ((uintptr_t)dst) | ((uintptr_t)w) | ((uintptr_t)bias)) & Pair<T>::MASK) == 0;
   const int half = rotary_dim >> 1;
@@ -103,7 +116,7 @@ __device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const 
         ss = fmaf(a[j], a[j], fmaf(b[j], b[j], ss));
       }
     }
-    const float rstd = !w ? 1.f : whole ? whole_rstd(whole, whole_bias, whole_n, eps, lane) : rsqrtf(warp_sum(ss) / (float)d + eps);
+    const float rstd = !w ? 1.f : given_rstd >= 0.f ? given_rstd : rsqrtf(warp_sum(ss) / (float)d + eps);
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < J; ++j) {
@@ -128,7 +141,7 @@ __device__ __forceinline__ void norm_rotate_head(const T* __restrict__ x, const 
     row[i] = w ? v * to_float(w[i]) : v;
     ss = fmaf(v, v, ss);
   }
-  const float rstd = !w ? 1.f : whole ? whole_rstd(whole, whole_bias, whole_n, eps, lane) : rsqrtf(warp_sum(ss) / (float)d + eps);
+  const float rstd = !w ? 1.f : given_rstd >= 0.f ? given_rstd : rsqrtf(warp_sum(ss) / (float)d + eps);
   __syncwarp();
   for (int i = lane; i < d; i += 32) {
     float y = row[i] * rstd;
@@ -149,7 +162,7 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, int q_stride, con
                                    const T* __restrict__ k_w, float eps, const float* __restrict__ cos_tab,
                                    const float* __restrict__ sin_tab, int rotary_dim, const int* __restrict__ slots,
                                    T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int num_tokens,
-                                   int heads, int kv_heads, int d, int dv, T* __restrict__ q_out, int norm_whole) {
+                                   int heads, int kv_heads, int d, int dv, T* __restrict__ q_out) {
   __shared__ float rows[QP_WARPS][QP_MAX_DIM];
   float* row = rows[threadIdx.x >> 5];
   pdl_trigger();
@@ -162,25 +175,16 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, int q_stride, con
   const float* cos_t = rotary_dim ? cos_tab + (size_t)t * (rotary_dim >> 1) : nullptr;
   const float* sin_t = rotary_dim ? sin_tab + (size_t)t * (rotary_dim >> 1) : nullptr;
   if (job < heads) {
-    if (norm_whole && q_w)
-      norm_rotate_head(q_in + (size_t)t * q_stride + job * d, q_b ? q_b + job * d : nullptr, q_w + job * d, eps, cos_t, sin_t,
-                       rotary_dim, d, q_out + ((size_t)t * heads + job) * d, lane, row, q_in + (size_t)t * q_stride, q_b, heads * d);
-    else
-      norm_rotate_head(q_in + (size_t)t * q_stride + job * d, q_b ? q_b + job * d : nullptr, q_w, eps, cos_t, sin_t, rotary_dim, d,
-                       q_out + ((size_t)t * heads + job) * d, lane, row);
+    norm_rotate_head(q_in + (size_t)t * q_stride + job * d, q_b ? q_b + job * d : nullptr, q_w, eps, cos_t, sin_t, rotary_dim, d,
+                     q_out + ((size_t)t * heads + job) * d, lane, row);
     return;
   }
   const int slot = slots[t];
   const int page = slot / page_size, off = slot - page * page_size;
   if (job < heads + kv_heads) {
     const int g = job - heads;
-    T* dst = k_cache + (((size_t)page * kv_heads + g) * page_size + off) * d;
-    if (norm_whole && k_w)
-      norm_rotate_head(k_in + (size_t)t * k_stride + g * d, k_b ? k_b + g * d : nullptr, k_w + g * d, eps, cos_t, sin_t,
-                       rotary_dim, d, dst, lane, row, k_in + (size_t)t * k_stride, k_b, kv_heads * d);
-    else
-      norm_rotate_head(k_in + (size_t)t * k_stride + g * d, k_b ? k_b + g * d : nullptr, k_w, eps, cos_t, sin_t, rotary_dim, d,
-                       dst, lane, row);
+    norm_rotate_head(k_in + (size_t)t * k_stride + g * d, k_b ? k_b + g * d : nullptr, k_w, eps, cos_t, sin_t, rotary_dim, d,
+                     k_cache + (((size_t)page * kv_heads + g) * page_size + off) * d, lane, row);
     return;
   }
   const int g = job - heads - kv_heads;
@@ -206,6 +210,67 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ q_in, int q_stride, con
   }
 }
 
+// The norm over the whole projection: a CTA per token. All its threads form the sums of squares of the token's q row
+// and k row once; then its warps take the heads in turn, each with the row's 1 / rms and its own stretch of the weight.
+constexpr int QW_WARPS = 8;
+template <typename T>
+__global__ void __launch_bounds__(QW_WARPS * 32) qkv_prepare_whole_kernel(
+    const T* __restrict__ q_in, int q_stride, const T* __restrict__ k_in, int k_stride, const T* __restrict__ v_in, int v_stride,
+    const T* __restrict__ q_b, const T* __restrict__ k_b, const T* __restrict__ v_b, const T* __restrict__ q_w,
+    const T* __restrict__ k_w, float eps, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int rotary_dim,
+    const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int heads, int kv_heads,
+    int d, int dv, T* __restrict__ q_out) {
+  __shared__ float rows[QW_WARPS][QP_MAX_DIM];
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* row = rows[warp];
+  float rstd_q = 1.f, rstd_k = 1.f;
+  if (q_w) rstd_q = rsqrtf(row_sumsq(q_in + (size_t)t * q_stride, q_b, heads * d, scratch) / (float)(heads * d) + eps);
+  if (k_in && k_w) rstd_k = rsqrtf(row_sumsq(k_in + (size_t)t * k_stride, k_b, kv_heads * d, scratch) / (float)(kv_heads * d) + eps);
+  const float* cos_t = rotary_dim ? cos_tab + (size_t)t * (rotary_dim >> 1) : nullptr;
+  const float* sin_t = rotary_dim ? sin_tab + (size_t)t * (rotary_dim >> 1) : nullptr;
+  const int jobs = heads + (k_in ? 2 * kv_heads : 0);
+  int page = 0, off = 0;
+  if (k_in) {
+    const int slot = slots[t];
+    page = slot / page_size;
+    off = slot - page * page_size;
+  }
+  for (int job = warp; job < jobs; job += QW_WARPS) {
+    if (job < heads) {
+      norm_rotate_head(q_in + (size_t)t * q_stride + job * d, q_b ? q_b + job * d : nullptr, q_w ? q_w + job * d : nullptr, eps,
+                       cos_t, sin_t, rotary_dim, d, q_out + ((size_t)t * heads + job) * d, lane, row, rstd_q);
+    } else if (job < heads + kv_heads) {
+      const int g = job - heads;
+      norm_rotate_head(k_in + (size_t)t * k_stride + g * d, k_b ? k_b + g * d : nullptr, k_w ? k_w + g * d : nullptr, eps, cos_t,
+                       sin_t, rotary_dim, d, k_cache + (((size_t)page * kv_heads + g) * page_size + off) * d, lane, row, rstd_k);
+    } else {
+      const int g = job - heads - kv_heads;
+      const T* src = v_in + (size_t)t * v_stride + g * dv;
+      T* dst = v_cache + (((size_t)page * kv_heads + g) * page_size + off) * dv;
+      const T* vb = v_b ? v_b + g * dv : nullptr;
+      if ((dv & 1) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst) | ((uintptr_t)vb)) & Pair<T>::MASK) == 0) {
+        for (int i = 2 * lane; i < dv; i += 64) {
+          float a, b;
+          Pair<T>::load(src + i, a, b);
+          if (vb) {
+            float ba, bb;
+            Pair<T>::load(vb + i, ba, bb);
+            a += ba;
+            b += bb;
+          }
+          Pair<T>::store(dst + i, a, b);
+        }
+      } else {
+        for (int i = lane; i < dv; i += 32) dst[i] = vb ? from_float<T>(to_float(src[i]) + to_float(vb[i])) : src[i];
+      }
+    }
+    __syncwarp();          // the warp's staging row is free for its next head
+  }
+}
+
 }  // namespace ts
 
 using namespace ts;
@@ -219,6 +284,19 @@ extern "C" int ts_qkv_prepare(const void* q_in, int q_stride, const void* k_in, 
   if (d > QP_MAX_DIM) return TS_ERR_UNSUPPORTED;
   if (rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || (rotary_dim && (!cos_tab || !sin_tab))) return TS_ERR_BAD_ARGUMENT;
   if (k_in && (!v_in || !slots || !k_cache || !v_cache || page_size <= 0)) return TS_ERR_BAD_ARGUMENT;
+  if (norm_whole) {
+    if (dtype == TS_DTYPE_F32)
+      return launch(qkv_prepare_whole_kernel<float>, num_tokens, QW_WARPS * 32, 0, stream, (const float*)q_in, q_stride,
+                    (const float*)k_in, k_stride, (const float*)v_in, v_stride, (const float*)q_b, (const float*)k_b, (const float*)v_b,
+                    (const float*)q_w, (const float*)k_w, eps, cos_tab, sin_tab, rotary_dim, slots, (float*)k_cache, (float*)v_cache,
+                    page_size, heads, kv_heads, d, dv, (float*)q_out);
+    if (dtype == TS_DTYPE_BF16)
+      return launch(qkv_prepare_whole_kernel<bf16>, num_tokens, QW_WARPS * 32, 0, stream, (const bf16*)q_in, q_stride,
+                    (const bf16*)k_in, k_stride, (const bf16*)v_in, v_stride, (const bf16*)q_b, (const bf16*)k_b, (const bf16*)v_b,
+                    (const bf16*)q_w, (const bf16*)k_w, eps, cos_tab, sin_tab, rotary_dim, slots, (bf16*)k_cache, (bf16*)v_cache,
+                    page_size, heads, kv_heads, d, dv, (bf16*)q_out);
+    return TS_ERR_BAD_ARGUMENT;
+  }
   const long long warps = (long long)num_tokens * (heads + (k_in ? 2 * kv_heads : 0));
   const int threads = QP_WARPS * 32;
   const int blocks = (int)((warps * 32 + threads - 1) / threads);
@@ -226,11 +304,11 @@ extern "C" int ts_qkv_prepare(const void* q_in, int q_stride, const void* k_in, 
     return launch(qkv_prepare_kernel<float>, blocks, threads, 0, stream, (const float*)q_in, q_stride, (const float*)k_in,
                   k_stride, (const float*)v_in, v_stride, (const float*)q_b, (const float*)k_b, (const float*)v_b, (const float*)q_w, (const float*)k_w, eps, cos_tab, sin_tab,
                   rotary_dim, slots, (float*)k_cache, (float*)v_cache, page_size, num_tokens, heads, kv_heads, d, dv,
-                  (float*)q_out, norm_whole);
+                  (float*)q_out);
   if (dtype == TS_DTYPE_BF16)
     return launch(qkv_prepare_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)q_in, q_stride, (const bf16*)k_in,
                   k_stride, (const bf16*)v_in, v_stride, (const bf16*)q_b, (const bf16*)k_b, (const bf16*)v_b, (const bf16*)q_w, (const bf16*)k_w, eps, cos_tab, sin_tab,
                   rotary_dim, slots, (bf16*)k_cache, (bf16*)v_cache, page_size, num_tokens, heads, kv_heads, d, dv,
-                  (bf16*)q_out, norm_whole);
+                  (bf16*)q_out);
   return TS_ERR_BAD_ARGUMENT;
 }

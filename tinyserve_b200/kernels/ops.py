@@ -50,7 +50,7 @@ _SIGNATURES: dict[str, list[Any]] = {
     "ts_softcap": [_vp, _c.c_size_t, _f, _vp],
     "ts_rms_norm_rows": [_vp, _c.c_longlong, _vp, _f, _vp, _i, _i, _i, _vp],
     "ts_head_norm_gate": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
-    "ts_post_norm_add_rms_norm": [_vp, _vp, _vp, _vp, _f, _i, _f, _vp, _i, _f, _vp, _vp, _i, _i, _i, _vp],
+    "ts_post_norm_add_rms_norm": [_vp, _vp, _vp, _vp, _f, _i, _f, _vp, _i, _f, _vp, _vp, _i, _i, _vp, _i, _vp],
     "ts_mlstm_scan": [_vp, _i, _i, _i, _i, _vp, _vp, _f, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp],
     "ts_delta_scan": [_vp, _i, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ts_causal_conv_silu": [_vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp],
@@ -238,10 +238,11 @@ def add_rms_norm(resid: torch.Tensor, delta: torch.Tensor | None, weight: torch.
 def post_norm_add_rms_norm(resid: torch.Tensor, delta: torch.Tensor | None, post_weight: torch.Tensor | None,
                            layer_scale: torch.Tensor | None, post_eps: float, post_offset: bool, weight: torch.Tensor,
                            offset: bool, eps: float, out: torch.Tensor, rows: torch.Tensor | None = None,
-                           post_mult: float = 1.0) -> None:
+                           post_mult: float = 1.0, delta_bias: torch.Tensor | None = None) -> None:
     """The residual sum with a norm on the pending sub-layer output, and the next norm, in one pass,
     all in 32-bit: ``y = post_mult * delta / sqrt(mean(delta^2) + post_eps) * gain(post_weight) * layer_scale``
-    (``post_weight`` / ``layer_scale`` ``None``: that factor is left out), ``x = resid + y``,
+    (``post_weight`` / ``layer_scale`` ``None``: that factor is left out; without a ``post_weight``, ``delta_bias``
+    (one value per column, dt) is added to ``delta`` first: ``y = (delta + delta_bias) * layer_scale``), ``x = resid + y``,
     ``out = dt(x / sqrt(mean(x^2) + eps) * gain(weight))`` with ``gain(w) = 1 + w`` when the matching
     ``offset`` flag is set, else ``w``. Without ``rows`` the sum is written back to ``resid``; with
     ``rows`` (int32) only those rows are read and ``resid`` stays."""
@@ -250,7 +251,9 @@ def post_norm_add_rms_norm(resid: torch.Tensor, delta: torch.Tensor | None, post
     dt = out.dtype
     if weight.shape != (h,) or out.shape[1] != h or (delta is not None and delta.shape != resid.shape):
         raise KernelError("post_norm_add_rms_norm: shape mismatch")
-    for name, v in (("post_weight", post_weight), ("layer_scale", layer_scale)):
+    if delta_bias is not None and post_weight is not None:
+        raise KernelError("post_norm_add_rms_norm: a bias on the pending output goes without a norm on it")
+    for name, v in (("post_weight", post_weight), ("layer_scale", layer_scale), ("delta_bias", delta_bias)):
         if v is not None and (delta is None or v.shape != (h,)):
             raise KernelError(f"post_norm_add_rms_norm: {name} needs a pending output and one value per column")
     if (rows is None and n != resid.shape[0]) or (rows is not None and rows.shape != (n,)):
@@ -258,8 +261,8 @@ def post_norm_add_rms_norm(resid: torch.Tensor, delta: torch.Tensor | None, post
     _check(_fn("ts_post_norm_add_rms_norm")(
         _dev(resid, "resid", torch.float32), _opt(delta, "delta", dt), _opt(post_weight, "post_weight", dt),
         _opt(layer_scale, "layer_scale", dt), float(post_eps), int(bool(post_offset)), float(post_mult), _dev(weight, "weight", dt),
-        int(bool(offset)), float(eps), _dev(out, "out"), _opt(rows, "rows", torch.int32), n, h, _code(dt), _stream()),
-        "post_norm_add_rms_norm")
+        int(bool(offset)), float(eps), _dev(out, "out"), _opt(rows, "rows", torch.int32), n, h, _opt(delta_bias, "delta_bias", dt),
+        _code(dt), _stream()), "post_norm_add_rms_norm")
 
 
 def rope_tables(positions: torch.Tensor, inv_freq: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:

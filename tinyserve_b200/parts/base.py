@@ -276,7 +276,8 @@ class ResidualStream:
 
     A layer that norms a sub-layer's output before the residual sum leaves that norm pending too:
     ``post`` holds ``(weight, layer_scale | None, eps, unit_offset, mult)`` with which ``delta`` is normed
-    and scaled when the next norm folds it into the stream (``parts.norm.PostRMSNorm``)."""
+    and scaled when the next norm folds it into the stream (``parts.norm.PostRMSNorm``); a sixth element, when
+    there is one, is an output bias of the sub-layer that is added to ``delta`` first (``parts.norm.LayerScale``)."""
 
     __slots__ = ("resid", "delta", "sumsq", "resid16", "_sumsq_buf", "_resid16_buf", "lanes", "connection", "post")
 

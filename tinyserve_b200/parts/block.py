@@ -47,7 +47,8 @@ class PreNormBlock(Block):
 class SandwichBlock(Block):
     """A norm before and after each sub-layer: ``x += post(mixer(norm(x)))`` and, when the layer has
     a feed-forward, ``x += post(feed_forward(norm(x)))``. The post norms (``PostRMSNorm``, which may
-    carry a layer scale) stay pending with the output and are applied by the next norm's kernel."""
+    carry a layer scale, or a ``LayerScale`` alone) stay pending with the output and are applied by the next
+    norm's kernel; a ``LayerScale`` also takes over the feed-forward's output bias."""
 
     roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm",
              "feed_forward_norm": "norm", "feed_forward": "feed_forward", "feed_forward_post_norm": "norm"}
@@ -71,7 +72,13 @@ class SandwichBlock(Block):
         p["mixer_post_norm"].leave(stream, p["mixer"].forward(hn, ctx, caches.get("mixer"), writes_cache, position))
         if "feed_forward" in p:
             hn = p["feed_forward_norm"].forward(stream, ctx)
-            p["feed_forward_post_norm"].leave(stream, p["feed_forward"].forward(hn, ctx))
+            ff, post = p["feed_forward"], p["feed_forward_post_norm"]
+            bias = getattr(ff, "output_bias", None)
+            if bias is not None and getattr(post, "accepts_bias", False):
+                # the feed-forward's output bias rides along with the pending output: no pass of its own
+                post.leave(stream, ff.forward(hn, ctx, add_output_bias=False), bias)
+            else:
+                post.leave(stream, ff.forward(hn, ctx))
 
 
 class ParallelResidualBlock(Block):

@@ -204,6 +204,11 @@ class RoutedExperts(FeedForward):
     def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
         p, n = prefix + self.prefix, self.names
         self.w_router = tensors[p + n["router"] + ("+" + n["shared"] + n["shared_gate"] if self.shared_gate else "")]
+        if self.scored and self.w_router.shape[0] % 16:
+            # zero rows up to a multiple of 16: the few-row product of decode steps takes such matrices
+            padded = torch.zeros((-(-self.w_router.shape[0] // 16) * 16, self.h), dtype=self.w_router.dtype, device=self.w_router.device)
+            padded[: self.w_router.shape[0]] = self.w_router
+            self.w_router = padded
         if self.scored:
             corr = tensors[p + n["correction"]].float().contiguous() if self.has_correction else None
             self.rule = ops.RouteRule(scored=True, groups=self.groups, keep=self.group_keep, scale=self.route_scale,

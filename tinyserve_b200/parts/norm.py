@@ -43,10 +43,11 @@ class RMSNorm(Norm):
         if stream.post is None and not self.round_once:
             ops.add_rms_norm(stream.resid, stream.delta, self.weight, self.eps, out, rows=rows)
             return
-        post_w, post_scale, post_eps, post_offset, post_mult = \
+        post_w, post_scale, post_eps, post_offset, post_mult, *rest = \
             stream.post if stream.post is not None else (None, None, 0.0, False, 1.0)
         ops.post_norm_add_rms_norm(stream.resid, stream.delta, post_w, post_scale, post_eps, post_offset, self.weight,
-                                   self.unit_offset, self.eps, out, rows=rows, post_mult=post_mult)
+                                   self.unit_offset, self.eps, out, rows=rows, post_mult=post_mult,
+                                   delta_bias=rest[0] if rest else None)
 
     def forward(self, stream: ResidualStream, ctx: StepContext) -> torch.Tensor:
         out = ctx.arena.take((stream.resid.shape[0], self.size), ctx.dtype)
@@ -110,7 +111,10 @@ class PostRMSNorm(Norm):
 class LayerScale(Norm):
     """No norm at all on a sub-layer's output, only a learned factor per column (tensor ``name``) and an
     optional constant ``mult``: ``leave(stream, y)`` leaves ``y`` pending with the factor, and the next norm's
-    kernel adds ``mult * scale * y`` to the 32-bit stream in the same pass as its own norm."""
+    kernel adds ``mult * scale * y`` to the 32-bit stream in the same pass as its own norm. ``leave(stream, y,
+    bias)`` takes over the sub-layer's output bias too (``accepts_bias``): the kernel adds ``scale * (y + bias)``."""
+
+    accepts_bias = True
 
     recordable = EVERY_STEP
 
@@ -126,11 +130,11 @@ class LayerScale(Norm):
     def bind(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
         self.scale = tensors[prefix + self.name]
 
-    def leave(self, stream: ResidualStream, y: torch.Tensor) -> None:
+    def leave(self, stream: ResidualStream, y: torch.Tensor, bias: torch.Tensor | None = None) -> None:
         if stream.delta is not None:
             raise RuntimeError("a sub-layer output is already pending on the stream")
         stream.delta = y
-        stream.post = (None, self.scale, 0.0, False, 1.0)
+        stream.post = (None, self.scale, 0.0, False, 1.0, bias)
         stream.sumsq = None
 
     def forward(self, stream: ResidualStream, ctx: StepContext) -> torch.Tensor:
