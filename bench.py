@@ -557,6 +557,8 @@ def main() -> int:
                     help="instead of the headline: prefill and decode throughput of a design (--design) beside Qwen3 at "
                          "equal layer sizes (bench_designs.py); with --kernels also each step's time by kernel class")
     ap.add_argument("--design", choices=["fegilix", "guzovik", "gasavik", "diderax"], default="fegilix", help="with --designs: the design measured beside Qwen3")
+    ap.add_argument("--design-beside", choices=["qwen3", "fegilix", "guzovik", "gasavik", "diderax"], default="qwen3",
+                    help="with --designs: the model the design is measured beside, at equal layer sizes")
     ap.add_argument("--design-sizes", default="", help="with --designs: layer sizes to run, e.g. 1k or 1k,4k (default: all)")
     args = ap.parse_args()
     if args.gpus != 1:

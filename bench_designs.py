@@ -1,7 +1,7 @@
-"""``python bench.py --designs [--design fegilix|guzovik|gasavik|diderax]``: prefill and decode throughput of a
-design at layer sizes that resemble a real model's (random weights), beside the dense Qwen3 decoder,
-the closest existing model, with the same width, attention heads, (active) feed-forward size and
-number of layers; and where each design's step time goes, kernel class by kernel class, with the
+"""``python bench.py --designs [--design fegilix|guzovik|gasavik|diderax] [--design-beside qwen3|guzovik|...]``:
+prefill and decode throughput of a design at layer sizes that resemble a real model's (random weights), beside
+the dense Qwen3 decoder (or, with ``--design-beside``, another design of the framework), with the same width,
+attention heads, (active) feed-forward size and number of layers; and where each design's step time goes, kernel class by kernel class, with the
 share of the measured peaks each class reaches. The default workload of ``bench.py`` does not come
 through here.
 
@@ -343,14 +343,15 @@ def run(args) -> int:
 
     pk, pk_src = peaks()
     tokens, batch, ctx = 2048, 8, 1024
-    design = getattr(args, "design", "fegilix")
-    result = {"metric": f"prefill and decode tok/s of {design.capitalize()} beside Qwen3 at equal layer sizes (6 layers, bf16, random weights)",
+    design, beside = getattr(args, "design", "fegilix"), getattr(args, "design_beside", "qwen3")
+    beside_config = qwen3_config if beside == "qwen3" else DESIGNS[beside]
+    result = {"metric": f"prefill and decode tok/s of {design.capitalize()} beside {beside.capitalize()} at equal layer sizes (6 layers, bf16, random weights)",
               "peaks": {**{k: pk[k] for k in ("hbm_gbs", "bf16_tflops")}, "source": pk_src},
               "workload": {"prefill_tokens": tokens, "decode_batch": batch, "decode_context": ctx, "page_size": PAGE}, "sizes": {}}
     for size in (args.design_sizes.split(",") if args.design_sizes else list(SIZES)):
         s = SIZES[size]
         entry = {}
-        for label, cfg in ((design, DESIGNS[design](s)), ("qwen3", qwen3_config(s))):
+        for label, cfg in ((design, DESIGNS[design](s)), (beside, beside_config(s))):
             b = DesignBench(cfg)
             pre = b.prefill_ms(tokens)
             dec, _, launches = b.device_decode(batch, ctx, max(args.warmup, 3), args.steps, check=False)
