@@ -93,12 +93,12 @@ def diderax_config(s: dict) -> dict:
     latents of 512 + 64 for keys and values and of three eighths of the width for the queries; linear-attention
     heads of 128 that fill the width."""
     attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
-            "rot": {"dims": s["dim"] // 2, "base": 250000.0, "scaling": {"factor": 8.0}}}
+            "rot": {"dims": s["dim"] // 2, "base": 5e5, "scaling": {"factor": 4.0}}}
     latent = {"heads": s["heads"], "dim": s["dim"], "rot_dim": 64, "vdim": s["dim"], "kv_rank": 512, "q_rank": 3 * s["width"] // 8,
-              "scale": (s["dim"] + 64) ** -0.5, "rot": {"dims": 64, "base": 250000.0}}
-    gla = {"heads": s["rec_heads"], "dim": s["dim"], "vdim": s["dim"], "tau": 16.0, "decay_rank": 64}
+              "scale": (s["dim"] + 64) ** -0.5, "rot": {"dims": 64, "base": 5e5}}
+    gla = {"heads": s["rec_heads"], "dim": s["dim"], "vdim": s["dim"], "tau": 8.0, "decay_rank": 64}
     ff = s["ff"] // 4
-    moe = {"kind": "moe", "router": {"experts": s["experts"], "identity": 4, "top": 3, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
+    moe = {"kind": "moe", "router": {"experts": s["experts"], "identity": 4, "top": 3, "scale": 2.0, "groups": {"count": 4, "keep": 2}},
            "expert": {"ff": ff}, "shared": {"ff": ff}}
     dense = {"kind": "dense", "ff": s["ff"]}
     return {"architecture": "Diderax", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-6}, "max_positions": 8192,

@@ -68,7 +68,7 @@ CONFIG_B = {
     "layers": [
         {"type": "latent_attention", "mixer": latent(2, 8, 8, 16, 24, 40, 0.25, 4, 1e4, 2.0), "mlp": moe(3, 3, 24, identity=3, groups=(2, 1), shared=16)},
         {"type": "gla", "mixer": gla(1, 40, 16, 16.0, 3), "mlp": dense(56)},
-        {"type": "attention", "mixer": attention(3, 3, 16, 0.25, 4, 250000.0, 8.0), "mlp": moe(6, 2, 8, groups=(3, 3), scale=0.5, shared=24)},
+        {"type": "attention", "mixer": attention(3, 3, 16, 0.25, 4, 300000.0, 6.0), "mlp": moe(6, 2, 8, groups=(3, 3), scale=0.5, shared=24)},
         {"type": "gla", "mixer": gla(3, 8, 8, 1.0, 12), "mlp": None},
     ],
 }
@@ -93,9 +93,9 @@ CONFIG_C = {
 CONFIG_D = {
     "architecture": "Diderax", "vocab": 211, "width": 128, "norm": {"eps": 1e-6},
     "layers": [
-        {"type": "attention", "mixer": attention(4, 2, 64, 0.06, 32, 250000.0, 8.0), "mlp": moe(8, 2, 64, identity=4, groups=(3, 2), scale=1.5, shared=128)},
-        {"type": "gla", "mixer": gla(2, 64, 64, 16.0, 16), "mlp": dense(256)},
-        {"type": "latent_attention", "mixer": latent(8, 32, 32, 48, 64, 48, 0.06, 32, 250000.0), "mlp": dense(128)},
+        {"type": "attention", "mixer": attention(4, 2, 64, 0.06, 32, 500000.0, 4.0), "mlp": moe(11, 2, 96, identity=1, groups=(3, 2), scale=1.25, shared=160)},
+        {"type": "gla", "mixer": gla(2, 64, 64, 12.0, 16), "mlp": dense(256)},
+        {"type": "latent_attention", "mixer": latent(6, 48, 32, 64, 64, 56, 0.06, 32, 500000.0), "mlp": dense(128)},
         {"type": "gla", "mixer": gla(1, 128, 32, 8.0, 8), "mlp": None},
         {"type": "attention", "mixer": attention(2, 1, 128, 0.04, 128, 1e4), "mlp": moe(4, 2, 128)},
     ],
@@ -111,11 +111,11 @@ def random_config(seed: int) -> dict:
     layers = []
     for _ in range(rng.randint(2, 5)):
         kind = rng.choice(["attention", "latent_attention", "gla"])
-        factor = rng.choice([None, 1.0, 2.0, 8.0])
+        factor = rng.choice([None, 1.0, 2.0, 6.0])
         if kind == "attention":
             groups, dim = rng.randint(1, 2), rng.choice([8, 16, 24, 32, 64])
             mixer = attention(groups * rng.randint(1, 3), groups, dim, rng.uniform(0.1, 0.4), rng.choice([2, dim // 2, dim]),
-                              rng.choice([100.0, 1e4, 250000.0]), factor)
+                              rng.choice([100.0, 1e4, 5e5]), factor)
         elif kind == "latent_attention":
             rot_dim = rng.choice([2, 8, 16])
             mixer = latent(rng.randint(1, 4), rng.choice([8, 16, 24]), rot_dim, rng.choice([8, 24, 32]), rng.choice([8, 16, 40]),

@@ -142,7 +142,7 @@ def _route_case(t, outputs, seed, spread=3.0):
 
 
 @pytest.mark.parametrize("outputs, identity, top, groups, keep, scale", [(8, 2, 3, 4, 2, 2.0), (6, 3, 3, 2, 1, 1.0), (2, 1, 1, 1, 1, 1.5),
-                                                                         (12, 0, 4, 3, 2, 0.5), (20, 4, 4, 2, 1, 1.5), (5, 0, 2, 1, 1, 1.0)])
+                                                                         (12, 0, 4, 3, 2, 0.5), (24, 6, 5, 3, 1, 1.75), (5, 0, 2, 1, 1, 1.0)])
 def test_reference_routing_against_the_plain_rule(outputs, identity, top, groups, keep, scale) -> None:
     t, width = 37, 16
     h = _rand(t, width, seed=1)

@@ -78,7 +78,7 @@ def test_norm_over_the_whole_projection_kernel(dtype, heads, groups, d, rotary) 
     pos = torch.arange(100, 100 + t, dtype=torch.float64)
     cos = sin = None
     if rotary:
-        ang = pos[:, None] * (1e4 ** (-torch.arange(0, rotary, 2, dtype=torch.float64) / rotary) / 8.0)[None, :]
+        ang = pos[:, None] * (1e4 ** (-torch.arange(0, rotary, 2, dtype=torch.float64) / rotary) / 6.0)[None, :]
         cos, sin = ang.cos().float().cuda(), ang.sin().float().cuda()
     slots = torch.randperm(8 * page, generator=torch.Generator().manual_seed(4))[:t].int().cuda()
     res = []
@@ -252,7 +252,7 @@ def test_gated_linear_scan_in_segments_of_several_lengths() -> None:
 
 @pytest.mark.parametrize("tokens", [1, 9, 64, 65, 700])
 @pytest.mark.parametrize("outputs, identity, top, groups, keep, scale", [(8, 2, 3, 4, 2, 2.0), (6, 3, 3, 2, 1, 1.0), (2, 1, 1, 1, 1, 1.5),
-                                                                         (12, 0, 4, 3, 2, 0.5), (20, 4, 4, 2, 1, 1.5), (5, 0, 2, 1, 1, 1.0),
+                                                                         (12, 0, 4, 3, 2, 0.5), (24, 6, 5, 3, 1, 1.75), (5, 0, 2, 1, 1, 1.0),
                                                                          (96, 32, 8, 32, 5, 2.5), (40, 0, 32, 1, 1, 1.0)])
 def test_scored_routing_kernel(tokens, outputs, identity, top, groups, keep, scale) -> None:
     """Picks, weights and the sorted order against the reference; the router's outputs are the first columns of
