@@ -476,7 +476,8 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
-  const float sg = shared_gate ? 1.f / (1.f + expf(-shared_gate[(size_t)t * gate_stride])) : 1.f;
+  // volatile: this read stands right behind the wait and depends on nothing, so as a plain read it could be moved in front of it
+  const float sg = shared_gate ? 1.f / (1.f + expf(-*(const volatile float*)(shared_gate + (size_t)t * gate_stride))) : 1.f;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float v = 0.f;
     for (int j = 0; j < top; ++j) {
@@ -498,7 +499,8 @@ __global__ void moe_combine_vec_kernel(const T* __restrict__ y, const int* __res
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
-  const float sg = shared_gate ? 1.f / (1.f + expf(-shared_gate[(size_t)t * gate_stride])) : 1.f;
+  // volatile: this read stands right behind the wait and depends on nothing, so as a plain read it could be moved in front of it
+  const float sg = shared_gate ? 1.f / (1.f + expf(-*(const volatile float*)(shared_gate + (size_t)t * gate_stride))) : 1.f;
   const int* rows = row_of + (size_t)t * top;
   const float* wt = weights + (size_t)t * top;
   for (int c = threadIdx.x * VEC; c < hidden; c += blockDim.x * VEC) {
