@@ -477,6 +477,61 @@ def test_a_far_token_decides_the_logits(folders) -> None:
     assert_rows_close(got[None], want[0][299:], want[1][299:], torch.float32, "far token")
 
 
+def _with_overlap(mask, fn):
+    """``fn()`` with the launch-overlap mask of every kind of step set to ``mask``."""
+    from tinyserve_b200.kernels import ops
+
+    saved = (ops.PREFILL_PDL_MASK, ops.SMALL_DECODE_PDL_MASK, ops.DEFAULT_PDL_MASK)
+    try:
+        ops.PREFILL_PDL_MASK = ops.SMALL_DECODE_PDL_MASK = ops.DEFAULT_PDL_MASK = mask
+        ops.set_programmatic_launch(mask)
+        return fn()
+    finally:
+        ops.PREFILL_PDL_MASK, ops.SMALL_DECODE_PDL_MASK, ops.DEFAULT_PDL_MASK = saved
+        ops.set_programmatic_launch(saved[2])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("which", ["A", "D"])
+def test_overlapping_launches_change_no_bit(folders, oracle, dtype, which) -> None:
+    """A kernel that starts while the kernels before it still run must read their results behind its wait: the
+    logits of mixed steps, decoded tokens and portions are equal bit for bit with the overlap on and off."""
+    from tinyserve_b200.model import DecoderModel
+
+    reqs, _ = oracle[which]
+    model = DecoderModel.from_folder(folders[which], dtype, "cuda")
+    long = list(reqs)[-1]
+    for steps in (cases.mixed(reqs, 5), cases.tail_decoded(long, reqs[long], 40), cases.portions(long, reqs[long], 3)):
+        rows = {}
+        for mask in (0, -1):
+            got, _ = _with_overlap(mask, lambda: run_steps(model, 16, steps, cases.max_live_tokens(steps)))
+            rows[mask] = torch.cat([torch.stack([got[r][p] for p in sorted(got[r])]) for r in sorted(got)])
+        assert torch.equal(rows[0], rows[-1])
+
+
+def test_a_long_prompt_at_a_real_width_with_overlapping_launches() -> None:
+    """2,048 tokens at width 1,024 through linear attention and experts with identity experts: the experts' products
+    run on sorted, gathered rows in tiles of 128, of which the identity picks own none. Two different prompts one
+    after the other on the same scratch, overlap on and off: equal bit for bit, and no row of garbage is looked up."""
+    from tinyserve_b200.config import config_from_dict
+    from tinyserve_b200.engine.replay import Replayer
+    from tinyserve_b200.model import DecoderModel
+
+    cfg = {"architecture": "Diderax", "vocab": 1000, "width": 1024, "norm": {"eps": 1e-6}, "layers": [
+        {"type": "gla", "mixer": {"heads": 8, "dim": 128, "vdim": 128, "tau": 8.0, "decay_rank": 64},
+         "mlp": {"kind": "moe", "router": {"experts": 16, "identity": 4, "top": 3, "scale": 2.0, "groups": {"count": 4, "keep": 2}},
+                 "expert": {"ff": 768}, "shared": {"ff": 768}}}]}
+    model = DecoderModel.from_config(config_from_dict(cfg), seed=1, dtype=torch.bfloat16, device="cuda")
+    prompts = [random_prompt(2048, 1000, s) for s in (1, 2)]
+
+    def run():
+        rep = Replayer(model, 4096, page_size=16, max_live=2)
+        return torch.cat([rep.run_step([(f"p{i}", p, [0, 1000, 2047])], [f"p{i}"]).clone() for i, p in enumerate(prompts)])
+
+    plain, overlapped = _with_overlap(0, run), _with_overlap(-1, run)
+    assert not plain.isnan().any() and torch.equal(plain, overlapped)
+
+
 @pytest.mark.parametrize("graphs", [True, False])
 @pytest.mark.parametrize("which", ["A", "D"])
 def test_greedy_generation_through_llm(folders, graphs, which) -> None:
